@@ -382,6 +382,11 @@ typedef struct {
     int32_t v_ld;                  /* elements between the value rows of a page (0: vdim). With v_pool == k_pool and v_ld == dim
                                       the values are the leading vdim numbers of the key rows (one latent vector per token that
                                       serves as key and as value) */
+    int32_t keep_first;            /* with a window: keys at positions < keep_first stay visible to every later query (at their
+                                      true positions); 0: none */
+    const float* sig_bias;         /* fp32 [n_heads] or NULL. Not NULL: no softmax; the weight of a visible key is
+                                      sigmoid(score + sig_bias[h]) and the weights are not normalised over the keys (sink unused) */
+    float out_scale;               /* factor on the head outputs (0 is read as 1) */
 } p3_attn_window_args;
 /* query rows per tile that p3_attn_window_prefill takes for these sizes: 64 on its tensor-core path, else 32 */
 int p3_attn_window_tile_rows(const p3_attn_window_args* args);
@@ -450,6 +455,79 @@ int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float*
 
 /* logits <- cap * tanh(logits * scale / cap) (cap <= 0: logits * scale), n numbers in place */
 int p3_logit_softcap(float* logits, int64_t n, float scale, float cap, cudaStream_t st);
+
+
+/* ---- parts of decoders with a norm before AND after every sublayer, a token shift in front of the mixer, rotated windowed
+ * attention (softmax with kept first tokens, or sigmoid weights over keys that double as values), a matrix-memory recurrence
+ * and a mixture of experts with identity experts (Dugalix and designs built from these parts). Recurrent layers keep their
+ * state per sequence slot; a step's sequences are described by `seqs`, int32 x 4 per sequence: {first batch row, number of
+ * rows, sequence slot, position of the first row}; a sequence whose first row has position 0 starts from the zero state
+ * whatever its slot holds. */
+
+/* y' = y + y_bias (y_bias fp32 [W] or NULL); x += y' / sqrt(mean(y'^2) + eps) * gain_post (y NULL: x stays as it is). Then, with
+ * gain_pre: h = x / sqrt(mean(x^2) + eps) * gain_pre -> h32 (fp32 [T, W], may be NULL) and h_act (activation type, may be NULL).
+ * The gains are complete factors: a weight stored around zero enters as 1 + w, a residual multiplier is folded into gain_post. */
+int p3_postnorm_prenorm(const float* y, int64_t ldy, const float* y_bias, const float* gain_post, float* x, const float* gain_pre,
+                        float* h32, void* h_act, int act_f32, int64_t T, int W, float eps, cudaStream_t st);
+
+/* out[t] = h[t] + (prev - h[t]) * shift, prev = h[t - 1] inside a sequence's rows, the slot's saved row for its first row
+ * (zeros at position 0); afterwards state[slot] = h[last row of the sequence]. state fp32 [slots][W]; slot_seq int32 [slots] =
+ * index of the slot's record in seqs for this step. */
+int p3_token_shift(const float* h, const float* shift, float* state, const int32_t* seqs, const int32_t* slot_seq,
+                   const int32_t* tok_slot, void* out, int out_f32, int64_t T, int W, cudaStream_t st);
+
+/* After a fused q|k|v projection (proj fp32 [T, ld_proj]; bias fp32 indexed like proj's columns, or NULL): the leading rot_n
+ * numbers of every query and key head turn by position * freq[i] (number i paired with i + rot_n / 2, freq fp32 [rot_n / 2]), the
+ * rest passes; q -> q_out (act), k -> K pool, v -> V pool. v_off < 0: there is no value projection, the value of a token is its key
+ * BEFORE the rotation (vdim == dim). */
+typedef struct {
+    const float* proj; int64_t ld_proj; int32_t q_off, k_off, v_off;
+    const float* bias;
+    int32_t n_heads, n_kv, dim, vdim, rot_n; const float* freq;
+    void* q_out; int64_t ld_q;
+    void* k_pool; void* v_pool; const int32_t* block_table; int32_t bt_stride;
+    const int32_t* tok_slot; const int32_t* tok_pos; int32_t T;
+    int32_t act_f32, cache_f32;
+} p3_qkv_rope_post_args;
+int p3_qkv_rope_post(const p3_qkv_rope_post_args* args, cudaStream_t st);
+
+/* out (act) [R, F] = max(u, 0)^2 * (row_gate ? sigmoid(row_gate[r * ld_gate]) : 1), u fp32 with row pitch ld */
+int p3_relu2(const float* u, int64_t ld, const float* row_gate, int64_t ld_gate, void* out, int64_t ldo, int out_f32, int64_t R, int F,
+             cudaStream_t st);
+
+/* Router over ready logits (fp32 [T, ld_logits], E outputs). mode bit 0: scores s = softmax over all E (else sigmoid); bit 1: a
+ * group's score is its largest choice score (else the sum of its two largest); bit 2: wts = s[ids] as they are (else
+ * s[ids] / (sum + 1e-20) * scale). choice = s + correction; groups and ties as in p3_router_sigmoid_groups. */
+int p3_router_groups(const float* logits, int64_t ld_logits, const float* correction, int T, int E, int top, int n_groups, int keep,
+                     float scale, int mode, int32_t* ids, float* wts, cudaStream_t st);
+
+/* out[t] = sum_j wts[t][j] * (ids[t][j] < n_real ? y[where[t * top + j]] : h[t]) + (add ? add[t] : 0): experts with an index of
+ * n_real or more are identity experts, whose output is the layer's input h (fp32 [T, W]); add fp32 [T, ld_add] or NULL */
+int p3_moe_combine_identity(const float* y, int64_t ldy, const int32_t* where, const int32_t* ids, const float* wts, int top,
+                            int n_real, const float* h, const float* add, int64_t ld_add, float* out, int64_t T, int W,
+                            cudaStream_t st);
+
+/* Matrix-memory recurrence (csrc/recurrent.cu). Per head: memory S [dim][vdim], normaliser n [dim], stabiliser m (0 at the start).
+ * From proj (fp32 [T, ld_proj]): q at q_off (times q_scale), k at k_off (heads x dim), v at v_off (heads x vdim), gate
+ * pre-activations at i_off and f_off (one per head, biases i_bias / f_bias fp32 [heads]).
+ *   a = cap tanh(pre_i / cap), b = logsigmoid(cap tanh(pre_f / cap)), m' = max(b + m, a),
+ *   S' = e^(b + m - m') S + e^(a - m') k v^T, n' alike with k, y = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6)
+ * token by token over the rows of every sequence of `seqs`; y -> out fp32 [T, ld_out], head h at column h * vdim. The state of a
+ * slot is `state + slot * p3_matrix_memory_state_floats(...)` floats, read at the start and written at the end of the step. */
+typedef struct {
+    const float* proj; int64_t ld_proj; int32_t q_off, k_off, v_off, i_off, f_off;
+    const float* i_bias; const float* f_bias;
+    int32_t n_heads, dim, vdim; float q_scale, gate_cap;
+    float* state; const int32_t* seqs; int32_t n_seqs;
+    float* out; int64_t ld_out;
+} p3_matrix_memory_args;
+int64_t p3_matrix_memory_state_floats(int n_heads, int dim, int vdim);
+int p3_matrix_memory_scan(const p3_matrix_memory_args* args, cudaStream_t st);
+
+/* out (act) [T, ldo] = y / sqrt(mean over the head's vdim numbers of y^2 + eps) * gain[c] * sigmoid(gate[t][c]) * scale, y fp32
+ * [T, ldy] with n_heads x vdim columns, gate fp32 logits [T, ld_gate] or NULL */
+int p3_headnorm_gate(const float* y, int64_t ldy, int n_heads, int vdim, const float* gain, const float* gate, int64_t ld_gate,
+                     float scale, float eps, void* out, int64_t ldo, int out_f32, int64_t T, cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -77,8 +77,18 @@ _SIGS = {
     'p3_glu_silu': [_p, _p, _l, _p, _l, _i, _l, _i, _p],
     'p3_router_sigmoid_groups': [_p, _l, _i, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p],
     'p3_logit_softcap': [_p, _l, _f, _f, _p],
+    # sandwich norms, token shift, relu^2 unit, softmax group router with identity experts, head norm of a recurrent mixer
+    # (csrc/seq_ops.cu, csrc/recurrent.cu)
+    'p3_postnorm_prenorm': [_p, _l, _p, _p, _p, _p, _p, _p, _i, _l, _i, _f, _p],
+    'p3_token_shift': [_p, _p, _p, _p, _p, _p, _p, _i, _l, _i, _p],
+    'p3_relu2': [_p, _l, _p, _l, _p, _l, _i, _l, _i, _p],
+    'p3_router_groups': [_p, _l, _p, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p],
+    'p3_moe_combine_identity': [_p, _l, _p, _p, _p, _i, _i, _p, _p, _l, _p, _l, _i, _p],
+    'p3_headnorm_gate': [_p, _l, _i, _i, _p, _p, _l, _f, _f, _p, _l, _i, _l, _p],
 }
-_STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode', 'p3_latent_post']
+ROUTER_SOFTMAX, ROUTER_GROUP_MAX, ROUTER_PLAIN_WEIGHTS = 1, 2, 4          # mode bits of p3_router_groups
+_STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode', 'p3_latent_post',
+                   'p3_qkv_rope_post', 'p3_matrix_memory_scan']
 ATTN_WINDOW_MMA = os.environ.get('P3_ATTN_WINDOW_MMA', '1') != '0'
 
 _lib = None
@@ -109,6 +119,7 @@ def lib():
             for name in _STRUCT_ENTRIES:
                 getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
             L.p3_attn_window_tile_rows.argtypes, L.p3_attn_window_tile_rows.restype = [_p], C.c_int
+            L.p3_matrix_memory_state_floats.argtypes, L.p3_matrix_memory_state_floats.restype = [_i, _i, _i], C.c_int64
             L.p3_last_error.restype = C.c_char_p
             L.p3_version.restype = C.c_int
             _lib = L
@@ -127,6 +138,7 @@ def lib():
         for name in _STRUCT_ENTRIES:                                                        # (const args*, stream)
             getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
         L.p3_attn_window_tile_rows.argtypes, L.p3_attn_window_tile_rows.restype = [_p], C.c_int
+        L.p3_matrix_memory_state_floats.argtypes, L.p3_matrix_memory_state_floats.restype = [_i, _i, _i], C.c_int64
         _lib = L
     return _lib
 
@@ -220,7 +232,8 @@ class AttnWindowArgs(C.Structure):
                 ('sink', _p), ('penalty', _p), ('n_penalty', C.c_int32), ('gate', _p), ('out', _p), ('ld_out', _l),
                 ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('scale', C.c_float),
                 ('window', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32), ('tiles', _p), ('n_tiles', C.c_int32),
-                ('n_splits', C.c_int32), ('ws', _p), ('v_ld', C.c_int32)]
+                ('n_splits', C.c_int32), ('ws', _p), ('v_ld', C.c_int32), ('keep_first', C.c_int32), ('sig_bias', _p),
+                ('out_scale', C.c_float)]
 
 
 class LatentPostArgs(C.Structure):
@@ -232,3 +245,20 @@ class LatentPostArgs(C.Structure):
                 ('q_plain', _p), ('ld_qp', _l), ('q_lat', _p), ('ld_ql', _l), ('hid', _p), ('ld_hid', _l), ('hid_off', C.c_int32),
                 ('cache', _p), ('block_table', _p), ('bt_stride', C.c_int32),
                 ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32)]
+
+
+class QkvRopePostArgs(C.Structure):
+    """p3_qkv_rope_post_args (include/phi3_b200.h)"""
+    _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('k_off', C.c_int32), ('v_off', C.c_int32), ('bias', _p),
+                ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('rot_n', C.c_int32),
+                ('freq', _p), ('q_out', _p), ('ld_q', _l),
+                ('k_pool', _p), ('v_pool', _p), ('block_table', _p), ('bt_stride', C.c_int32),
+                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32)]
+
+
+class MatrixMemoryArgs(C.Structure):
+    """p3_matrix_memory_args (include/phi3_b200.h)"""
+    _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('k_off', C.c_int32), ('v_off', C.c_int32),
+                ('i_off', C.c_int32), ('f_off', C.c_int32), ('i_bias', _p), ('f_bias', _p),
+                ('n_heads', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('q_scale', C.c_float), ('gate_cap', C.c_float),
+                ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l)]

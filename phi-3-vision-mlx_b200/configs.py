@@ -260,3 +260,114 @@ def tiny_tapalix(width=96, vocab=300, layers=None, loop=(1, 3, 2), eps=1e-5):
     if loop:
         d['loop'] = {'start': loop[0], 'stop': loop[1], 'times': loop[2]}
     return d
+
+
+# ------------------------------------------------------------------------------------------------ Dugalix
+class DugalixConfig:
+    """config.json of a Dugalix checkpoint: {"architecture": "Dugalix", "vocab", "width", "norm": {"eps"}, "residual_mult",
+    "layers": [...]}. A layer entry has "type", "mixer" and "mlp":
+      type "attention": mixer = {heads, kv_heads, dim, vdim, scale, mask: {size}, rot: {base, dims}}: the values are the keys before
+                        their rotation (vdim == dim) and a visible key weighs sigmoid(score + per-head bias);
+      type "parallel":  mixer = {left: {heads, kv_heads, dim, vdim, scale, mask: {size, keep_first}, rot: {base, dims, scaling:
+                        {factor}}}, right: {heads, dim, vdim, gate_cap}, left_scale, right_scale}: softmax attention with biases
+                        beside a matrix-memory recurrence;
+      mlp: null | {"kind": "dense", ff} | {"kind": "moe", expert: {ff}, router: {experts, identity, top, groups: {count, keep}},
+                        shared: {ff}}: `identity` further router outputs stand for experts that return their input.
+    Absent optional keys mean: no window, no kept first tokens, no rotation, no slowing factor, no groups, no identity experts, no
+    shared unit. Nothing is assumed equal between layers."""
+    @staticmethod
+    def _attention(i, m, kind):
+        mask, r = m.get('mask') or {}, m.get('rot')
+        a = SimpleNamespace(kind=kind, heads=int(m['heads']), kv_heads=int(m.get('kv_heads', m['heads'])), dim=int(m['dim']),
+                            vdim=int(m.get('vdim', m['dim'])), scale=float(m['scale']), window=int(mask.get('size') or 0),
+                            keep_first=int(mask.get('keep_first') or 0), rot=None)
+        if a.heads % a.kv_heads:
+            raise ValueError(f'layer {i}: heads must be a multiple of kv_heads')
+        if r and int(r.get('dims', a.dim)) > 0:
+            a.rot = SimpleNamespace(base=float(r['base']), dims=int(r.get('dims', a.dim)),
+                                    factor=float((r.get('scaling') or {}).get('factor', 1.0)))
+            if a.rot.dims % 2 or a.rot.dims > a.dim:
+                raise ValueError(f'layer {i}: rot.dims must be even and at most dim')
+        if kind == 'sigmoid' and a.vdim != a.dim:
+            raise ValueError(f'layer {i}: keys that double as values need vdim == dim')
+        return a
+
+    def __init__(self, d):
+        self.raw = d
+        self.architecture = d.get('architecture', 'Dugalix')
+        self.architectures = [self.architecture]
+        self.vocab_size, self.width = int(d['vocab']), int(d['width'])
+        self.eps = float(d['norm']['eps'])
+        self.residual_mult = float(d.get('residual_mult', 1.0))
+        self.layers = []
+        for i, lc in enumerate(d['layers']):
+            kind, m = lc.get('type'), lc['mixer']
+            if kind == 'attention':
+                mixer = SimpleNamespace(kind=kind, att=self._attention(i, m, 'sigmoid'), mem=None, att_scale=1.0, mem_scale=0.0)
+            elif kind == 'parallel':
+                r = m['right']
+                mem = SimpleNamespace(heads=int(r['heads']), dim=int(r['dim']), vdim=int(r.get('vdim', r['dim'])),
+                                      gate_cap=float(r['gate_cap']))
+                if not 1 <= mem.dim <= 256:
+                    raise NotImplementedError(f'layer {i}: matrix-memory key size {mem.dim}; the kernels take 1 .. 256')
+                mixer = SimpleNamespace(kind=kind, att=self._attention(i, m['left'], 'softmax'), mem=mem,
+                                        att_scale=float(m.get('left_scale', 1.0)), mem_scale=float(m.get('right_scale', 1.0)))
+            else:
+                raise NotImplementedError(f'layer {i}: mixer type {kind!r} is not part of this design')
+            f = lc.get('mlp')
+            if f is None:
+                ff = None
+            elif f['kind'] == 'dense':
+                ff = SimpleNamespace(kind='dense', ff=int(f['ff']))
+            elif f['kind'] == 'moe':
+                r = f['router']
+                g = r.get('groups') or {}
+                ff = SimpleNamespace(kind='moe', ff=int(f['expert']['ff']), experts=int(r['experts']), identity=int(r.get('identity') or 0),
+                                     top=int(r['top']), groups=int(g.get('count', 1)), keep=int(g.get('keep', 1)),
+                                     shared_ff=int((f.get('shared') or {}).get('ff', 0)))
+                ff.outputs = ff.experts + ff.identity          # what the router scores
+                if not 1 <= ff.top <= ff.outputs:
+                    raise ValueError(f'layer {i}: top must be in [1, experts + identity]')
+                if ff.groups > 1 and (ff.outputs % ff.groups or not 1 <= ff.keep <= ff.groups
+                                      or ff.keep * (ff.outputs // ff.groups) < ff.top):
+                    raise ValueError(f'layer {i}: expert groups must divide experts + identity and the kept ones must hold `top`')
+            else:
+                raise NotImplementedError(f"layer {i}: feed-forward kind {f['kind']!r}")
+            self.layers.append(SimpleNamespace(mixer=mixer, ff=ff))
+        self.num_hidden_layers = len(self.layers)
+
+    def kv_layout(self):
+        """per layer (kv heads, key size, value size): what the page pool allocates (every layer has an attention)"""
+        return [(l.mixer.att.kv_heads, l.mixer.att.dim, l.mixer.att.vdim) for l in self.layers]
+
+
+def rot_frequencies(rot):
+    """angular frequency of every turning pair: base^(-2i/dims), divided by the slowing factor"""
+    return [rot.base ** (-2.0 * i / rot.dims) / rot.factor for i in range(rot.dims // 2)]
+
+
+def tiny_dugalix(width=96, vocab=300, layers=None, eps=1e-5, residual_mult=0.7):
+    """A small Dugalix config dict for tests: sizes deliberately unequal between layers and between the halves of a parallel mixer
+    (dim != vdim, heads != kv_heads, partly rotated heads, windows and kept prefixes that differ), one layer without a
+    feed-forward, a mixture without groups / identity experts / shared unit beside one with all three."""
+    rot = lambda dims, factor=None: {'base': 10000.0, 'dims': dims, **({'scaling': {'factor': factor}} if factor else {})}
+    sig = lambda heads, kv, dim, win, rd, scale=None: {
+        'type': 'attention', 'mixer': dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=scale or dim ** -0.5,
+                                           mask={'size': win}, rot=rot(rd))}
+    par = lambda lh, lkv, ld, lv, win, keep, rd, rh, rdim, rv, ls=0.8, rs=1.1, factor=4.0, cap=15.0: {
+        'type': 'parallel',
+        'mixer': {'left': dict(heads=lh, kv_heads=lkv, dim=ld, vdim=lv, scale=ld ** -0.5, mask={'size': win, 'keep_first': keep},
+                               rot=rot(rd, factor)),
+                  'right': dict(heads=rh, dim=rdim, vdim=rv, gate_cap=cap), 'left_scale': ls, 'right_scale': rs}}
+    dense = lambda ff: {'kind': 'dense', 'ff': ff}
+    moe = lambda ff, e, ident, top, groups=None, shared=None: {
+        'kind': 'moe', 'expert': {'ff': ff},
+        'router': dict(experts=e, identity=ident, top=top, **({'groups': {'count': groups[0], 'keep': groups[1]}} if groups else {})),
+        **({'shared': {'ff': shared}} if shared else {})}
+    if layers is None:
+        layers = [dict(par(6, 3, 24, 40, 37, 5, 16, 3, 24, 40), mlp=moe(40, 5, 3, 3, (4, 3), 72)),
+                  dict(sig(4, 2, 40, 33, 24), mlp=dense(136)),
+                  dict(par(4, 1, 32, 16, 70, 66, 32, 2, 40, 72, factor=None), mlp=None),
+                  dict(sig(3, 3, 24, 90, 8), mlp=moe(32, 4, 0, 2))]
+    return {'architecture': 'Dugalix', 'vocab': vocab, 'width': width, 'norm': {'eps': eps}, 'residual_mult': residual_mult,
+            'layers': layers}

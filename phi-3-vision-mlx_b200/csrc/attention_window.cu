@@ -31,6 +31,19 @@ template <> __device__ __forceinline__ void stv<bf16>(bf16* p, float v) { *p = _
 constexpr int BQ = 32, WARPS = 4, RPW = BQ / WARPS;          // prefill: query rows per CTA / per warp
 constexpr int WIDE = 256;                                    // fp32 kernels: key numbers per chunk, value columns per CTA
 
+// The pages a tile of queries visits: those of the kept first tokens that lie before the window's pages, then the pages from
+// the first key inside the first row's window to the last row's own position.
+struct PageWalk {
+    int keep, n_keep, lo, n;
+    __device__ PageWalk(const p3_attn_window_args& a, int first, int last) {
+        keep = a.window > 0 ? a.keep_first : 0;              // without a window every earlier key is visible anyway
+        lo = first / P3_PAGE;
+        n_keep = min((keep + P3_PAGE - 1) / P3_PAGE, lo);
+        n = n_keep + last / P3_PAGE - lo + 1;
+    }
+    __device__ __forceinline__ int page(int it) const { return it < n_keep ? it : lo + it - n_keep; }
+};
+
 template <typename AT, typename CT, int DVC>
 __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn_window_args a) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
@@ -69,7 +82,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     const int first = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
     const float* pen = a.penalty ? a.penalty + (size_t)h * a.n_penalty : nullptr;
-    for (int pg = first / P3_PAGE; pg <= last / P3_PAGE; pg++) {
+    const bool sig = a.sig_bias != nullptr;                  // sigmoid weights: no running maximum, no denominator
+    const float sbias = sig ? a.sig_bias[h] : 0.f;
+    const PageWalk walk(a, first, last);
+    for (int it = 0; it < walk.n; it++) {
+        const int pg = walk.page(it);
         const int page = bt[pg];
         const CT* kp = (const CT*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
         const CT* vp = (const CT*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld + vc0;
@@ -110,11 +127,17 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const int kpos = pg * P3_PAGE + lane + 32 * e, dist = qpos - kpos;
-                const bool vis = qr < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
+                const bool vis = qr < nq && dist >= 0 && (a.window <= 0 || dist < a.window || kpos < walk.keep);
                 float v = -FLT_MAX;
                 if (vis) v = s[r][e] - (pen ? pen[min(dist, a.n_penalty - 1)] : 0.f);
                 pv[e] = v;
                 tmax = fmaxf(tmax, v);
+            }
+            if (sig) {
+#pragma unroll
+                for (int e = 0; e < 2; e++)
+                    Ss[qr * (P3_PAGE + 4) + lane + 32 * e] = pv[e] > -FLT_MAX ? 1.0f / (1.0f + expf(-(pv[e] + sbias))) : 0.f;
+                continue;
             }
             tmax = warp_max(tmax);
             const float mn = fmaxf(m[r], tmax);
@@ -156,8 +179,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     for (int r = 0; r < RPW; r++) {
         const int qr = warp * RPW + r;
         if (qr >= nq) continue;
-        const float gate = a.gate ? a.gate[(size_t)(row0 + qr) * a.n_heads + h] : 1.f;
-        const float inv = l[r] > 0.f ? gate / l[r] : 0.f;
+        const float gate = (a.gate ? a.gate[(size_t)(row0 + qr) * a.n_heads + h] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
+        const float inv = sig ? gate : (l[r] > 0.f ? gate / l[r] : 0.f);
 #pragma unroll
         for (int j = 0; j < DVC; j++) {
             const int c = lane + 32 * j;
@@ -414,8 +437,12 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
     const int g = blockIdx.y / v_parts, split = blockIdx.z, n_splits = gridDim.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int per = (((pos - first + 1) + n_splits - 1) / n_splits + 31) & ~31;
-    const int k_lo = first + split * per, k_hi = min(pos + 1, k_lo + per);
+    // the visible keys in one running index: the kept first tokens that lie before the window, then the window
+    const int n_keep = a.window > 0 ? min(a.keep_first, first) : 0, n_vis = n_keep + pos - first + 1;
+    const int per = ((n_vis + n_splits - 1) / n_splits + 31) & ~31;
+    const int k_lo = split * per, k_hi = min(n_vis, k_lo + per);
+    auto key_at = [&](int c) { return c < n_keep ? c : first + c - n_keep; };
+    const bool sig = a.sig_bias != nullptr;                  // sigmoid weights: the maximum is pinned at 0, the sum is not used
     const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
     const AT* q = (const AT*)a.q + (size_t)row * a.ld_q;
     const bool vec = (d % 8 == 0) && (((uintptr_t)a.k_pool & 15) == 0);
@@ -433,8 +460,8 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
             for (int j = 0; j < DVC; j++) acc[r][j] = 0.f;
         }
         for (int kb = k_lo + warp * 32; kb < k_hi; kb += DW * 32) {
-            const int kpos = kb + lane;
-            const bool valid = kpos < k_hi;
+            const bool valid = kb + lane < k_hi;
+            const int kpos = key_at(kb + lane);
             float s[RMAX];
 #pragma unroll
             for (int r = 0; r < RMAX; r++) s[r] = 0.f;
@@ -469,6 +496,12 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
                 if (r >= nr) continue;
                 float sv = -FLT_MAX;
                 if (valid) sv = s[r] - (a.penalty ? a.penalty[(size_t)(hb + r) * a.n_penalty + min(dist, a.n_penalty - 1)] : 0.f);
+                if (sig) {
+                    p[r] = valid ? 1.0f / (1.0f + expf(-(sv + a.sig_bias[hb + r]))) : 0.f;
+                    l[r] += p[r];
+                    m[r] = 0.f;
+                    continue;
+                }
                 const float mn = fmaxf(m[r], warp_max(sv)), corr = expf(m[r] - mn);
                 p[r] = valid ? expf(sv - mn) : 0.f;
                 l[r] = l[r] * corr + p[r];
@@ -482,7 +515,7 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
                 float vr[VR][DVC];
 #pragma unroll
                 for (int u = 0; u < VR; u++) {
-                    const int kp2 = min(kb + k0 + u, k_hi - 1);
+                    const int kp2 = key_at(min(kb + k0 + u, k_hi - 1));
                     const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * vld + vc0;
 #pragma unroll
                     for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; vr[u][j] = c < dv ? ldv(vp + c) : 0.f; }
@@ -520,8 +553,8 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
                 o = fmaf(As[(size_t)(w * RMAX + r) * dv + c], f, o);
             }
             if (n_splits == 1) {
-                const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
-                stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c, L > 0.f ? o * gate / L : 0.f);
+                const float gate = (a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
+                stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c, L > 0.f ? o * gate / (sig ? 1.f : L) : 0.f);
             } else {
                 float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (a.vdim + 2);
                 if (c == 0 && vc0 == 0) { w[0] = M; w[1] = L; }            // every column block forms the same maximum and sum
@@ -759,7 +792,8 @@ __global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, in
     const int t = blockIdx.x / a.n_heads, h = blockIdx.x % a.n_heads, dv = a.vdim;
     const int row = reinterpret_cast<const int4*>(a.tiles)[t].x;
     const float* w = a.ws + ((size_t)t * a.n_heads + h) * n_splits * (dv + 2);
-    const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + h] : 1.f;
+    const float gate = (a.gate ? a.gate[(size_t)row * a.n_heads + h] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
+    const bool sig = a.sig_bias != nullptr;                  // sigmoid weights: the slices' vectors add up, nothing divides
     float M = -FLT_MAX;
 #pragma unroll 4
     for (int s = 0; s < n_splits; s++) M = fmaxf(M, w[(size_t)s * (dv + 2)]);
@@ -773,7 +807,7 @@ __global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, in
             L = fmaf(ls, f, L);
             o = fmaf(os, f, o);
         }
-        stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)h * dv + c, L > 0.f ? o * gate / L : 0.f);
+        stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)h * dv + c, L > 0.f ? o * gate / (sig ? 1.f : L) : 0.f);
     }
 }
 
@@ -784,6 +818,8 @@ int check_args(const p3_attn_window_args* a, const char* who) {
     P3_CHECK_ARG(!a->penalty || a->n_penalty >= 1, "%s: empty penalty table", who);
     P3_CHECK_ARG(a->act_f32 == a->cache_f32, "%s: activations and cache must both be fp32 or both bf16", who);
     P3_CHECK_ARG(a->v_ld == 0 || a->v_ld >= a->vdim, "%s: the value row pitch must hold a value row", who);
+    P3_CHECK_ARG(a->keep_first >= 0, "%s: keep_first must not be negative", who);
+    P3_CHECK_ARG(!a->sig_bias || !a->sink, "%s: sigmoid weights have no denominator for a sink", who);
     return 0;
 }
 
@@ -830,7 +866,7 @@ int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
 static bool prefill_mma_ok(const p3_attn_window_args* a) {
     static int off = -1;
     if (off < 0) { const char* e = getenv("P3_ATTN_WINDOW_MMA"); off = (e && e[0] == '0') ? 1 : 0; }
-    return !off && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 256 && a->vdim <= 256 &&
+    return !off && !a->keep_first && !a->sig_bias && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 256 && a->vdim <= 256 &&
            a->ld_q % 2 == 0 && a->ld_out % 2 == 0 && ((uintptr_t)a->q & 3) == 0 && ((uintptr_t)a->out & 3) == 0 &&
            ((uintptr_t)a->k_pool & 15) == 0 && ((uintptr_t)a->v_pool & 15) == 0 && a->v_ld % 8 == 0;
 }

@@ -524,7 +524,7 @@ template <typename AT>
 __global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t ldx, const float* __restrict__ Wr,
                                              const float* __restrict__ corr, const float* __restrict__ logits, int64_t ld_logits,
                                              int W, int E, int top, int n_groups, int keep,
-                                             float scale, int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                             float scale, int mode, int32_t* __restrict__ ids, float* __restrict__ wts) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ float z[];                             // [E] scores s, [E] choice scores, [groups] group scores, [warps][8] partial sums
@@ -535,11 +535,7 @@ __global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t l
     float* part = gsc + NG;
     const AT* xr = x + (size_t)t * ldx;
     if (logits) {                                            // the logits came out of an earlier product (fp32 accumulation)
-        for (int e = threadIdx.x; e < E; e += blockDim.x) {
-            const float sg = 1.0f / (1.0f + expf(-logits[(size_t)t * ld_logits + e]));
-            z[e] = sg;
-            ch[e] = sg + (corr ? corr[e] : 0.f);
-        }
+        for (int e = threadIdx.x; e < E; e += blockDim.x) z[e] = logits[(size_t)t * ld_logits + e];
         __syncthreads();
     } else
     for (int e0 = 0; e0 < E; e0 += 8) {
@@ -563,18 +559,30 @@ __global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t l
         if (threadIdx.x < ne) {
             float v = 0.f;
             for (int w = 0; w < nw; w++) v += part[w * 8 + threadIdx.x];
-            const float sg = 1.0f / (1.0f + expf(-v));
-            z[e0 + threadIdx.x] = sg;
-            ch[e0 + threadIdx.x] = sg + (corr ? corr[e0 + threadIdx.x] : 0.f);
+            z[e0 + threadIdx.x] = v;
         }
         __syncthreads();
     }
     if (warp != 0) return;
+    // logits -> scores: sigmoid of each, or (mode bit 0) softmax over all outputs with sums in a fixed order
+    float zmax = -INFINITY, zsum = 0.f;
+    if (mode & 1) {
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = warp_max(zmax);
+        for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
+        zsum = warp_sum(zsum);
+    }
+    for (int e = lane; e < E; e += 32) {
+        const float sc = (mode & 1) ? expf(z[e] - zmax) / zsum : 1.0f / (1.0f + expf(-z[e]));
+        z[e] = sc;
+        ch[e] = sc + (corr ? corr[e] : 0.f);
+    }
+    __syncwarp();
     if (NG > 1) {
         for (int g = lane; g < NG; g += 32) {                // a group's score: its two largest choice scores
             float b1 = -INFINITY, b2 = -INFINITY;
             for (int e = g * gs; e < (g + 1) * gs; e++) { const float c = ch[e]; if (c > b1) { b2 = b1; b1 = c; } else if (c > b2) b2 = c; }
-            gsc[g] = gs > 1 ? b1 + b2 : b1;
+            gsc[g] = (gs > 1 && !(mode & 2)) ? b1 + b2 : b1;
         }
         __syncwarp();
         for (int k = 0; k < keep; k++) {                     // mark the kept groups by +inf, one arg-max per kept group
@@ -597,6 +605,7 @@ __global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t l
         den += z[bi];
         __syncwarp();
     }
+    if (mode & 4) return;                                    // the chosen scores are the weights as they are
     const float f = scale / (den + 1e-20f);
     for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= f;
 }
@@ -608,6 +617,176 @@ __global__ void logit_softcap_kernel(float* __restrict__ lg, int64_t n, float sc
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const float v = lg[i] * scale;
         lg[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+    }
+}
+
+// ---------------------------------------------------------------- norm after a sublayer, residual add, norm before the next one
+// x += rms_norm(y + bias) * gain_post, then h = rms_norm(x) * gain_pre: two row statistics in one pass over the row, which stays in
+// registers in between (up to RPT elements per thread; longer rows go through the row of x itself).
+template <typename AT>
+__global__ void postnorm_prenorm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ ybias,
+                                        const float* __restrict__ gpost, float* x, const float* __restrict__ gpre,
+                                        float* __restrict__ h32, AT* __restrict__ ha, int W, float eps) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    __shared__ float sh[32];
+    const int64_t t = blockIdx.x;
+    float* xr = x + (size_t)t * W;
+    const int nt = blockDim.x;
+    float xv[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; xv[k] = i < W ? xr[i] : 0.f; }
+    if (y) {
+        const float* yr = y + (size_t)t * ldy;
+        float v[RPT], gv[RPT];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            const int i = threadIdx.x + k * nt;
+            v[k] = i < W ? yr[i] + (ybias ? ybias[i] : 0.f) : 0.f;
+            gv[k] = i < W ? gpost[i] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < RPT; k++) ss = fmaf(v[k], v[k], ss);
+        for (int i = threadIdx.x + RPT * nt; i < W; i += nt) { const float u = yr[i] + (ybias ? ybias[i] : 0.f); ss = fmaf(u, u, ss); }
+        ss = block_sum(ss, sh);
+        const float r = 1.0f / sqrtf(ss / (float)W + eps);
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            const int i = threadIdx.x + k * nt;
+            if (i < W) { xv[k] = xv[k] + v[k] * r * gv[k]; xr[i] = xv[k]; }
+        }
+        for (int i = threadIdx.x + RPT * nt; i < W; i += nt) xr[i] = xr[i] + (yr[i] + (ybias ? ybias[i] : 0.f)) * r * gpost[i];
+    }
+    if (!gpre) return;
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < RPT; k++) s2 = fmaf(xv[k], xv[k], s2);
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) { const float u = xr[i]; s2 = fmaf(u, u, s2); }   // this thread's own writes
+    s2 = block_sum(s2, sh);
+    const float r2 = 1.0f / sqrtf(s2 / (float)W + eps);
+#pragma unroll
+    for (int k = 0; k < RPT; k++) {
+        const int i = threadIdx.x + k * nt;
+        if (i < W) { const float u = xv[k] * r2 * gpre[i]; if (h32) h32[(size_t)t * W + i] = u; if (ha) stv(ha + (size_t)t * W + i, u); }
+    }
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) {
+        const float u = xr[i] * r2 * gpre[i];
+        if (h32) h32[(size_t)t * W + i] = u;
+        if (ha) stv(ha + (size_t)t * W + i, u);
+    }
+}
+
+// ---------------------------------------------------------------- token shift: a row is blended with the row of the token before it
+// One CTA per row. The CTA of a sequence's first row reads the slot's saved row and then replaces it by the sequence's last
+// row of this step (same thread, same element: read before write), so no other CTA touches the slot's state.
+template <typename AT>
+__global__ void token_shift_kernel(const float* __restrict__ h, const float* __restrict__ shift, float* state,
+                                   const int32_t* __restrict__ seqs, const int32_t* __restrict__ slot_seq,
+                                   const int32_t* __restrict__ tok_slot, AT* __restrict__ out, int W) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int64_t t = blockIdx.x;
+    const int slot = tok_slot[t];
+    const int4 rec = reinterpret_cast<const int4*>(seqs)[slot_seq[slot]];   // {first row, rows, slot, first position}
+    const bool first = t == rec.x;
+    float* sv = state + (size_t)slot * W;
+    const float* hr = h + (size_t)t * W;
+    const float* prev = first ? (rec.w > 0 ? sv : nullptr) : hr - W;
+    const float* lastr = h + (size_t)(rec.x + rec.y - 1) * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float hv = hr[i], pv = prev ? prev[i] : 0.f;
+        stv(out + (size_t)t * W + i, hv + (pv - hv) * shift[i]);
+        if (first) sv[i] = lastr[i];
+    }
+}
+
+// ---------------------------------------------------------------- rotation of q and k + paged K/V write (+ projection biases)
+// Grid (token, job group): one warp per head job (H query heads, G key heads, G value heads when there is a value projection).
+// The lane that owns number i < rot_n / 2 of a head also owns its partner i + rot_n / 2; angles are position * frequency in fp32
+// with the full-range sincosf. Without a value projection the key head is written twice: rotated to the K pool, as projected to
+// the V pool.
+template <typename AT, typename CT>
+__global__ void qkv_rope_kv_write_kernel(p3_qkv_rope_post_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* pr = a.proj + (size_t)t * a.ld_proj;
+    const int slot = a.tok_slot[t], pos = a.tok_pos[t];
+    const int page = a.block_table[(size_t)slot * a.bt_stride + pos / P3_PAGE], off = pos % P3_PAGE;
+    const int H = a.n_heads, G = a.n_kv, d = a.dim, dv = a.vdim, half = a.rot_n / 2;
+    const bool v_is_k = a.v_off < 0;
+    const int jobs = H + G + (v_is_k ? 0 : G);
+    for (int job = blockIdx.y * nw + warp; job < jobs; job += gridDim.y * nw) {
+        if (job < H + G) {
+            const bool isq = job < H;
+            const int h = isq ? job : job - H;
+            const int col0 = (isq ? a.q_off : a.k_off) + h * d;
+            const float* src = pr + col0;
+            const float* b = a.bias ? a.bias + col0 : nullptr;
+            AT* dq = isq ? (AT*)a.q_out + (size_t)t * a.ld_q + (size_t)h * d : nullptr;
+            CT* dk = isq ? nullptr : (CT*)a.k_pool + (((size_t)page * G + h) * P3_PAGE + off) * d;
+            CT* dvv = (!isq && v_is_k) ? (CT*)a.v_pool + (((size_t)page * G + h) * P3_PAGE + off) * dv : nullptr;
+            for (int i = lane; i < d; i += 32) {
+                if (i >= half && i < a.rot_n) continue;      // the partner of a turning pair: written by the pair's owner
+                const float u = src[i] + (b ? b[i] : 0.f);
+                if (i < half) {
+                    const float w = src[i + half] + (b ? b[i + half] : 0.f);
+                    float sn, cs;
+                    sincosf((float)pos * a.freq[i], &sn, &cs);
+                    const float r0 = u * cs - w * sn, r1 = w * cs + u * sn;
+                    if (isq) { stv(dq + i, r0); stv(dq + i + half, r1); }
+                    else { stv(dk + i, r0); stv(dk + i + half, r1); if (dvv) { stv(dvv + i, u); stv(dvv + i + half, w); } }
+                } else {
+                    if (isq) stv(dq + i, u);
+                    else { stv(dk + i, u); if (dvv) stv(dvv + i, u); }
+                }
+            }
+        } else {
+            const int h = job - H - G, col0 = a.v_off + h * dv;
+            CT* dst = (CT*)a.v_pool + (((size_t)page * G + h) * P3_PAGE + off) * dv;
+            for (int i = lane; i < dv; i += 32) stv(dst + i, pr[col0 + i] + (a.bias ? a.bias[col0 + i] : 0.f));
+        }
+    }
+}
+
+// ---------------------------------------------------------------- out = max(u, 0)^2 (* sigmoid of a per-row gate logit)
+template <typename AT>
+__global__ void relu2_kernel(const float* __restrict__ u, int64_t ld, const float* __restrict__ row_gate, int64_t ld_gate,
+                             AT* __restrict__ out, int64_t ldo, int64_t R, int F) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int64_t n = R * F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F;
+        const int c = (int)(i - r * F);
+        const float v = fmaxf(u[r * ld + c], 0.f);
+        const float g = row_gate ? 1.0f / (1.0f + expf(-row_gate[r * ld_gate])) : 1.f;
+        stv(out + r * ldo + c, v * v * g);
+    }
+}
+
+// ---------------------------------------------------------------- weighted sum of the chosen experts, identity experts and an addend
+__global__ void moe_combine_identity_kernel(const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ where,
+                                            const int32_t* __restrict__ ids, const float* __restrict__ wts, int top, int n_real,
+                                            const float* __restrict__ h, const float* __restrict__ add, int64_t ld_add,
+                                            float* __restrict__ out, int W) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    extern __shared__ float cw[];                            // [top] weights, then [top] sorted rows (-1: identity expert)
+    int* rows = reinterpret_cast<int*>(cw + top);
+    const int64_t t = blockIdx.x;
+    for (int j = threadIdx.x; j < top; j += blockDim.x) {
+        cw[j] = wts[t * top + j];
+        rows[j] = ids[t * top + j] < n_real ? where[t * top + j] : -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float s = 0.f;
+        const float hv = h ? h[(size_t)t * W + i] : 0.f;
+#pragma unroll 4
+        for (int j = 0; j < top; j++) s = fmaf(cw[j], rows[j] >= 0 ? y[(size_t)rows[j] * ldy + i] : hv, s);
+        out[(size_t)t * W + i] = s + (add ? add[(size_t)t * ld_add + i] : 0.f);
     }
 }
 }  // namespace
@@ -779,8 +958,8 @@ extern "C" int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, c
     if (T == 0) return 0;
     const int nw = logits ? 1 : (W >= 1024 ? 8 : 4);         // with ready logits one warp per token does everything
     const size_t sm = ((size_t)2 * E + NG + nw * 8) * sizeof(float);
-    if (x_f32) p3_launch_pdl(router_sigmoid_groups_kernel<float>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const float*)x, ldx, Wr, correction, logits, ld_logits, W, E, top, NG, keep, scale, ids, wts);
-    else p3_launch_pdl(router_sigmoid_groups_kernel<bf16>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const bf16*)x, ldx, Wr, correction, logits, ld_logits, W, E, top, NG, keep, scale, ids, wts);
+    if (x_f32) p3_launch_pdl(router_sigmoid_groups_kernel<float>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const float*)x, ldx, Wr, correction, logits, ld_logits, W, E, top, NG, keep, scale, 0, ids, wts);
+    else p3_launch_pdl(router_sigmoid_groups_kernel<bf16>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const bf16*)x, ldx, Wr, correction, logits, ld_logits, W, E, top, NG, keep, scale, 0, ids, wts);
     P3_CHECK_LAUNCH("router_sigmoid_groups");
     return 0;
 }
@@ -790,5 +969,81 @@ extern "C" int p3_logit_softcap(float* logits, int64_t n, float scale, float cap
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
     p3_launch_pdl(logit_softcap_kernel, dim3(grid), dim3(256), (size_t)(0), st, logits, n, scale, cap);
     P3_CHECK_LAUNCH("logit_softcap");
+    return 0;
+}
+
+extern "C" int p3_router_groups(const float* logits, int64_t ld_logits, const float* correction, int T, int E, int top, int n_groups,
+                                int keep, float scale, int mode, int32_t* ids, float* wts, cudaStream_t st) {
+    P3_CHECK_ARG(logits && ids && wts, "router_groups: null argument");
+    P3_CHECK_ARG(top >= 1 && top <= E && E <= 1024, "router_groups: need 1 <= top <= outputs <= 1024");
+    const int NG = n_groups > 1 ? n_groups : 1;
+    P3_CHECK_ARG(E % NG == 0 && (NG == 1 || (keep >= 1 && keep <= NG && keep * (E / NG) >= top)),
+                 "router_groups: groups must divide the outputs and the kept groups must hold `top` of them");
+    if (T == 0) return 0;
+    const size_t sm = ((size_t)2 * E + NG + 8) * sizeof(float);
+    p3_launch_pdl(router_sigmoid_groups_kernel<float>, dim3((unsigned)T), dim3(32), (size_t)(sm), st, (const float*)nullptr, (int64_t)0,
+                  (const float*)nullptr, correction, logits, ld_logits, 0, E, top, NG, keep, scale, mode, ids, wts);
+    P3_CHECK_LAUNCH("router_groups");
+    return 0;
+}
+
+extern "C" int p3_postnorm_prenorm(const float* y, int64_t ldy, const float* y_bias, const float* gain_post, float* x,
+                                   const float* gain_pre, float* h32, void* h_act, int act_f32, int64_t T, int W, float eps,
+                                   cudaStream_t st) {
+    P3_CHECK_ARG(x && (!y || gain_post), "postnorm_prenorm: null argument");
+    if (T == 0) return 0;
+    const int th = W > 4096 ? 1024 : W > 2048 ? 512 : W >= 1024 ? 256 : 128;
+    if (act_f32) p3_launch_pdl(postnorm_prenorm_kernel<float>, dim3((unsigned)T), dim3(th), (size_t)(0), st, y, ldy, y_bias, gain_post, x, gain_pre, h32, (float*)h_act, W, eps);
+    else p3_launch_pdl(postnorm_prenorm_kernel<bf16>, dim3((unsigned)T), dim3(th), (size_t)(0), st, y, ldy, y_bias, gain_post, x, gain_pre, h32, (bf16*)h_act, W, eps);
+    P3_CHECK_LAUNCH("postnorm_prenorm");
+    return 0;
+}
+
+extern "C" int p3_token_shift(const float* h, const float* shift, float* state, const int32_t* seqs, const int32_t* slot_seq,
+                              const int32_t* tok_slot, void* out, int out_f32, int64_t T, int W, cudaStream_t st) {
+    P3_CHECK_ARG(h && shift && state && seqs && slot_seq && tok_slot && out, "token_shift: null argument");
+    P3_CHECK_ARG(((uintptr_t)seqs & 15) == 0, "token_shift: the sequence records must be 16-byte aligned");
+    if (T == 0) return 0;
+    const int th = W >= 2048 ? 256 : 128;
+    if (out_f32) p3_launch_pdl(token_shift_kernel<float>, dim3((unsigned)T), dim3(th), (size_t)(0), st, h, shift, state, seqs, slot_seq, tok_slot, (float*)out, W);
+    else p3_launch_pdl(token_shift_kernel<bf16>, dim3((unsigned)T), dim3(th), (size_t)(0), st, h, shift, state, seqs, slot_seq, tok_slot, (bf16*)out, W);
+    P3_CHECK_LAUNCH("token_shift");
+    return 0;
+}
+
+extern "C" int p3_qkv_rope_post(const p3_qkv_rope_post_args* a, cudaStream_t st) {
+    P3_CHECK_ARG(a && a->proj && a->q_out && a->k_pool && a->v_pool && a->block_table && a->tok_slot && a->tok_pos, "qkv_rope_post: null argument");
+    P3_CHECK_ARG(a->rot_n >= 0 && a->rot_n % 2 == 0 && a->rot_n <= a->dim && (a->rot_n == 0 || a->freq), "qkv_rope_post: rot_n must be even and <= dim, with frequencies");
+    P3_CHECK_ARG(a->v_off >= 0 || a->vdim == a->dim, "qkv_rope_post: keys that double as values need vdim == dim");
+    if (a->T == 0) return 0;
+    const int jobs = a->n_heads + a->n_kv + (a->v_off < 0 ? 0 : a->n_kv), th = 128;
+    const int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
+    const dim3 grid((unsigned)a->T, (unsigned)groups);
+    if (a->act_f32 && a->cache_f32) p3_launch_pdl(qkv_rope_kv_write_kernel<float, float>, dim3(grid), dim3(th), (size_t)(0), st, *a);
+    else if (!a->act_f32 && !a->cache_f32) p3_launch_pdl(qkv_rope_kv_write_kernel<bf16, bf16>, dim3(grid), dim3(th), (size_t)(0), st, *a);
+    else P3_CHECK_ARG(false, "qkv_rope_post: activations and cache must both be fp32 or both bf16");
+    P3_CHECK_LAUNCH("qkv_rope_post");
+    return 0;
+}
+
+extern "C" int p3_relu2(const float* u, int64_t ld, const float* row_gate, int64_t ld_gate, void* out, int64_t ldo, int out_f32,
+                        int64_t R, int F, cudaStream_t st) {
+    if (R == 0 || F == 0) return 0;
+    const int64_t n = R * F;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (out_f32) p3_launch_pdl(relu2_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, u, ld, row_gate, ld_gate, (float*)out, ldo, R, F);
+    else p3_launch_pdl(relu2_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), st, u, ld, row_gate, ld_gate, (bf16*)out, ldo, R, F);
+    P3_CHECK_LAUNCH("relu2");
+    return 0;
+}
+
+extern "C" int p3_moe_combine_identity(const float* y, int64_t ldy, const int32_t* where, const int32_t* ids, const float* wts, int top,
+                                       int n_real, const float* h, const float* add, int64_t ld_add, float* out, int64_t T, int W,
+                                       cudaStream_t st) {
+    P3_CHECK_ARG(y && where && ids && wts && out, "moe_combine_identity: null argument");
+    if (T == 0) return 0;
+    p3_launch_pdl(moe_combine_identity_kernel, dim3((unsigned)T), dim3(W >= 1024 ? 256 : 128), (size_t)(2 * top * sizeof(float)), st,
+                  y, ldy, where, ids, wts, top, n_real, h, add, ld_add, out, W);
+    P3_CHECK_LAUNCH("moe_combine_identity");
     return 0;
 }

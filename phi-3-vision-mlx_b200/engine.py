@@ -13,7 +13,10 @@ row ends. This engine serves a stream of requests instead:
                               single decoded tokens of the running requests, samples on the device with the framework's
                               p3_row_stats / p3_top_p_sample kernels, and frees a request's pages the step it finishes.
 
-A model plugs in with kv_layout(), cache_dtype(), prepare(max_context) and forward(StepBatch, pool) (tagenex.TagenexB200).
+A model plugs in with kv_layout(), cache_dtype(), prepare(max_context) and forward(StepBatch, pool) (tagenex.TagenexB200), and
+with state_layout() when its layers carry a recurrent state per sequence (dugalix.DugalixB200): the pool then keeps one row of
+fp32 numbers per slot and state buffer, and the step's descriptors list the sequences of the step (first row, rows, slot, first
+position) for the kernels that walk a sequence's rows in order.
 """
 import os
 
@@ -33,7 +36,9 @@ def _stream():
 class Engine:
     def __init__(self, model, max_tokens, n_slots=4):
         self.model, self.dev = model, model.dev
-        self.pool = PagePool(model.kv_layout(), max_tokens, n_slots, model.cache_dtype(), self.dev)
+        state_layout = model.state_layout() if hasattr(model, 'state_layout') else ()
+        self.pool = PagePool(model.kv_layout(), max_tokens, n_slots, model.cache_dtype(), self.dev, state_layout)
+        self.stateful = bool(state_layout)                   # recurrent layers: a request's tokens of a step are ONE run of rows
         model.prepare(self.pool.n_pages * PAGE)
         self.q_tile = int(getattr(model, 'q_tile', 32))      # query rows per CTA of the model's prefill attention kernel
         self.slot_of = {}                                    # request id -> slot
@@ -75,7 +80,10 @@ class Engine:
         need = sum(pool.pages_needed(self.slot_of[r], n) if r in self.slot_of else -(-n // PAGE) for r, n in grow.items())
         if need > len(pool.free_pages):
             raise PoolExhausted(f'page pool exhausted: the step wants {need} pages, {len(pool.free_pages)} of {pool.n_pages} free')
-        ids, slots, poss, pf, dec, want = [], [], [], [], [], []
+        if self.stateful and any(n > 1 for n in (sum(1 for r, t, _ in entries if r == rid and len(t)) for rid in grow)):
+            raise ValueError('a request may bring its tokens of a step in one entry only: its recurrent state advances once per step')
+        ids, slots, poss, pf, dec, want, seqs = [], [], [], [], [], [], []
+        slot_seq = [0] * pool.n_slots                        # slot -> its record in seqs (slots without tokens are never looked up)
         row = 0
         for rid, toks, wanted in entries:
             n = len(toks)
@@ -88,6 +96,8 @@ class Engine:
             ids.extend(int(t) for t in toks)
             slots.extend([s] * n)
             poss.extend(range(p0, p0 + n))
+            slot_seq[s] = len(seqs)
+            seqs.append((row, n, s, p0))
             if n == 1:
                 dec.append((row, 1, s, p0))
             else:
@@ -100,13 +110,14 @@ class Engine:
             row += n
         T = row
         b = StepBatch()
-        b.T, b.n_pf, b.n_dec, b.R = T, len(pf), len(dec), len(want)
+        b.T, b.n_pf, b.n_dec, b.R, b.n_seq, b.n_slots = T, len(pf), len(dec), len(want), len(seqs), pool.n_slots
         b.max_pos = max(poss) if poss else 0
         if T == 0:
             return b
         flat = np.concatenate([np.asarray(ids, np.int32), np.asarray(slots, np.int32), np.asarray(poss, np.int32),
                                np.asarray(pf, np.int32).reshape(-1), np.asarray(dec, np.int32).reshape(-1),
-                               np.asarray(want, np.int32)])
+                               np.asarray(seqs, np.int32).reshape(-1), np.asarray(want, np.int32),
+                               np.asarray(slot_seq, np.int32)])
         pad = (-3 * T) % 4                                   # tile records are read as 16-byte vectors
         flat = np.concatenate([flat[:3 * T], np.zeros(pad, np.int32), flat[3 * T:]])
         d = torch.from_numpy(flat).to(self.dev)
@@ -126,7 +137,11 @@ class Engine:
         o += 4 * b.n_pf
         b.dec_tiles = d[o:o + 4 * b.n_dec]
         o += 4 * b.n_dec
+        b.seqs = d[o:o + 4 * b.n_seq]                        # {first row, rows, slot, first position} per sequence of the step
+        o += 4 * b.n_seq
         b.want_rows = d[o:o + b.R]
+        o += b.R
+        b.slot_seq = d[o:o + b.n_slots]
 
     def step(self, entries, end=(), trace=None):
         """-> fp32 logits [number of wanted rows, vocab] on the device (None if nothing is wanted), rows in the order of the
@@ -158,6 +173,7 @@ class Engine:
         if 'graph' not in ent:
             sb = StepBatch()
             sb.T, sb.n_pf, sb.n_dec, sb.R, sb.max_pos = b.T, 0, b.n_dec, b.R, b.max_pos
+            sb.n_seq, sb.n_slots = b.n_seq, b.n_slots
             self._bind(sb, torch.empty_like(b.flat))
             sb.flat.copy_(b.flat)
             torch.cuda.synchronize()

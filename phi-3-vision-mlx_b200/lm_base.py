@@ -34,7 +34,8 @@ def _page_slices(pairs, pages, slots=2 * 148, merge=0.0):
 
 class StepBatch:
     """Device-side description of one engine step (built by engine.Engine.step)."""
-    __slots__ = ('T', 'ids', 'tok_slot', 'tok_pos', 'pf_tiles', 'n_pf', 'dec_tiles', 'n_dec', 'want_rows', 'R', 'max_pos', 'flat')
+    __slots__ = ('T', 'ids', 'tok_slot', 'tok_pos', 'pf_tiles', 'n_pf', 'dec_tiles', 'n_dec', 'want_rows', 'R', 'max_pos', 'flat',
+                 'seqs', 'n_seq', 'slot_seq', 'n_slots')
 
 
 class PagedLM:
@@ -117,16 +118,21 @@ class PagedLM:
         return out
 
     # ------------------------------------------------------------------ mixture of experts behind a router
-    def experts(self, gu_w, down_w, f, xa, y, T, ids, wts, glu):
+    def experts(self, gu_w, down_w, f, xa, y, T, ids, wts, glu, n_sorted=None, combine=None):
         """ids / wts [T, top] from the design's router -> y fp32 [T, W] = sum of the chosen experts' outputs. gu_w [E, 2 ff, W] holds
         every expert's gate rows over its up rows, down_w [E, W, ff]; glu(gu fp32 [n, 2 ff], hid act [n, ff], n) is the design's
-        activation. The (token, choice) pairs are sorted by expert and run as two grouped products over the sorted rows."""
+        activation. The (token, choice) pairs are sorted by expert and run as two grouped products over the sorted rows.
+        A unit without a gate passes its up matrices alone ([E, ff, W]; the activation then gets [n, ff]). n_sorted: the router
+        scores this many outputs, of which only the first f.experts have matrices (the pairs of the others are sorted behind them
+        and skipped by the products); combine(dn, where) then replaces the plain weighted sum."""
         st, dev, n = _stream(), self.dev, T * f.top
-        seg = torch.empty(f.experts + 1, dtype=torch.int32, device=dev)
+        n_sorted = f.experts if n_sorted is None else n_sorted
+        up = gu_w.shape[1]
+        seg = torch.empty(n_sorted + 1, dtype=torch.int32, device=dev)
         order = torch.empty(n, dtype=torch.int32, device=dev)
         where = torch.empty(n, dtype=torch.int32, device=dev)
-        call('p3_moe_sort', ptr(ids), n, f.experts, ptr(seg), ptr(order), ptr(where), st)
-        gu = torch.empty((n, 2 * f.ff), dtype=torch.float32, device=dev)
+        call('p3_moe_sort', ptr(ids), n, n_sorted, ptr(seg), ptr(order), ptr(where), st)
+        gu = torch.empty((n, up), dtype=torch.float32, device=dev)
         hid = torch.empty((n, f.ff), dtype=self.dtype, device=dev)
         dn = torch.empty((n, self.W), dtype=torch.float32, device=dev)
         # Large batches (prompt portions): the segment offsets are read back (one small D2H per mixture layer) and every expert's
@@ -142,10 +148,10 @@ class PagedLM:
                 a0, a1 = cut[ex], cut[ex + 1]
                 if a1 > a0:
                     call('p3_gemm', ptr(xs[a0:a1]), xs.stride(0), ptr(gu_w[ex]), gu_w.stride(1), None, ptr(gu[a0:a1]), gu.stride(0),
-                         None, None, a1 - a0, 2 * f.ff, self.W, _lib.EPI_F32, 0, st)
+                         None, None, a1 - a0, up, self.W, _lib.EPI_F32, 0, st)
         else:
             self.gemm_any(xa, gu_w, gu, rows=order, row_div=f.top, seg=seg, n_groups=f.experts, M=n)
-        self._ev(ev, 'moe_gemm', 2 * n * 2 * f.ff * self.W, gu_w.numel() * gu_w.element_size())
+        self._ev(ev, 'moe_gemm', 2 * n * up * self.W, gu_w.numel() * gu_w.element_size())
         glu(gu, hid, n)
         ev = self._ev()
         if dense:
@@ -157,7 +163,10 @@ class PagedLM:
         else:
             self.gemm_any(hid, down_w, dn, seg=seg, n_groups=f.experts, M=n)
         self._ev(ev, 'moe_gemm', 2 * n * f.ff * self.W, down_w.numel() * down_w.element_size())
-        call('p3_moe_combine', ptr(dn), dn.stride(0), ptr(where), ptr(wts), f.top, ptr(y), T, self.W, st)
+        if combine is not None:
+            combine(dn, where)
+        else:
+            call('p3_moe_combine', ptr(dn), dn.stride(0), ptr(where), ptr(wts), f.top, ptr(y), T, self.W, st)
 
     def experts_dense(self, f, T):
         """do the experts of a step with T tokens run as dense per-expert products (which reads the segment offsets back)?"""

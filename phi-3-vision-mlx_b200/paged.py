@@ -9,6 +9,11 @@ Per layer there is one K pool [page][kv heads][64][key size] and one V pool [pag
 differ between layers (`layout` = [(kv_heads, key size, value size), ...]). Pools are zero-initialised and only ever hold finite
 numbers, so a masked slot can never poison a weighted sum. The block table lives on the device; the host keeps a mirror and
 uploads the rows that changed before a step.
+
+Recurrent state. A model whose layers carry a state from token to token (a token shift, a matrix memory) names the fp32 numbers
+each of its state buffers needs per sequence (`state_layout` = [numbers per slot, ...]); the pool allocates them once as
+[slots][numbers] and a sequence's state lives in the row of its slot. Nothing is cleared when a slot changes hands: the kernels
+start a sequence whose first token has position 0 from the zero state whatever the row holds.
 """
 import torch
 
@@ -20,14 +25,16 @@ class PoolExhausted(RuntimeError):
 
 
 class PagePool:
-    def __init__(self, layout, max_tokens, n_slots, dtype, device):
+    def __init__(self, layout, max_tokens, n_slots, dtype, device, state_layout=()):
         self.layout, self.dtype, self.dev = list(layout), dtype, torch.device(device)
+        self.state_layout = [int(n) for n in state_layout]
         self.n_pages = max(1, -(-int(max_tokens) // PAGE))
         self.n_slots = int(n_slots)
         self.k = [torch.zeros((self.n_pages, g, PAGE, d), dtype=dtype, device=self.dev) for g, d, _ in self.layout]
         self.v = [torch.zeros((self.n_pages, g, PAGE, dv), dtype=dtype, device=self.dev) for g, _, dv in self.layout]
         self.bt_host = torch.zeros((self.n_slots, self.n_pages), dtype=torch.int32)
         self.block_table = torch.zeros((self.n_slots, self.n_pages), dtype=torch.int32, device=self.dev)
+        self.state = [torch.zeros((self.n_slots, n), dtype=torch.float32, device=self.dev) for n in self.state_layout]
         self.free_pages = list(range(self.n_pages - 1, -1, -1))      # pop() hands out page 0 first
         self.free_slots = list(range(self.n_slots - 1, -1, -1))
         self.pages = {}                                              # slot -> page ids in sequence order

@@ -96,7 +96,19 @@ def _tapalix_build(cfg, weights, device='cuda', dtype=None, **kw):
     return TapalixB200(cfg, weights, device=device, dtype=dtype or torch.bfloat16)
 
 
+def _dugalix_config(d):
+    from .configs import DugalixConfig
+    return DugalixConfig(d)
+
+
+def _dugalix_build(cfg, weights, device='cuda', dtype=None, **kw):
+    import torch
+    from .dugalix import DugalixB200
+    return DugalixB200(cfg, weights, device=device, dtype=dtype or torch.bfloat16)
+
+
 register('Phi3ForCausalLM', _phi3_config, _phi3_build, 'batch')
 register('Phi3VForCausalLM', _phi3_config, _phi3_build, 'batch')
 register('Tagenex', _tagenex_config, _tagenex_build, 'paged')
 register('Tapalix', _tapalix_config, _tapalix_build, 'paged')
+register('Dugalix', _dugalix_config, _dugalix_build, 'paged')

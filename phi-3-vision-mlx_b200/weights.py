@@ -210,3 +210,87 @@ def random_tapalix_weights(cfg, seed=0, device='cpu'):
             t = rn(shape) / shape[-1] ** 0.5
         w[name] = t.to(torch.bfloat16)
     return w
+
+
+def dugalix_tensor_shapes(cfg):
+    """name -> shape of every tensor of a Dugalix checkpoint; cfg = the config.json dict"""
+    W, V = cfg['width'], cfg['vocab']
+    out = {'embed': (V, W)}
+
+    def attention(p, m, biased, values):
+        H, G, d = m['heads'], m.get('kv_heads', m['heads']), m['dim']
+        dv = m.get('vdim', d)
+        out.update({p + 'q': (H * d, W), p + 'k': (G * d, W)})
+        if values:
+            out[p + 'v'] = (G * dv, W)
+        out[p + 'o'] = (W, H * dv)
+        if biased:
+            out.update({p + 'q.b': (H * d,), p + 'k.b': (G * d,), p + 'v.b': (G * dv,), p + 'o.b': (W,)})
+        else:
+            out[p + 'pb'] = (H,)
+
+    for i, lc in enumerate(cfg['layers']):
+        p, m = f'l{i}.', lc['mixer']
+        out.update({p + 'norm1': (W,), p + 'norm1b': (W,), p + 'shift': (W,)})
+        if lc['type'] == 'parallel':
+            attention(p + 'mix.left.', m['left'], True, True)
+            r = m['right']
+            H, d = r['heads'], r['dim']
+            dv = r.get('vdim', d)
+            q = p + 'mix.right.'
+            out.update({q + 'q': (H * d, W), q + 'k': (H * d, W), q + 'v': (H * dv, W), q + 'g': (H * dv, W), q + 'o': (W, H * dv),
+                        q + 'norm': (H * dv,), q + 'i': (H, W), q + 'i.b': (H,), q + 'f': (H, W), q + 'f.b': (H,)})
+        else:
+            attention(p + 'mix.', m, False, False)
+        f = lc.get('mlp')
+        if f is None:
+            continue
+        out.update({p + 'norm2': (W,), p + 'norm2b': (W,)})
+        if f['kind'] == 'dense':
+            out.update({p + 'mlp.up': (f['ff'], W), p + 'mlp.down': (W, f['ff'])})
+            continue
+        F, E = f['expert']['ff'], f['router']['experts']
+        n_out = E + int(f['router'].get('identity') or 0)
+        for e in range(E):
+            out.update({f'{p}mlp.e{e}.up': (F, W), f'{p}mlp.e{e}.down': (W, F)})
+        out.update({p + 'mlp.router': (n_out, W), p + 'mlp.correction': (n_out,)})
+        if f.get('shared'):
+            S = f['shared']['ff']
+            out.update({p + 'mlp.shared.up': (S, W), p + 'mlp.shared.down': (W, S), p + 'mlp.shared.sg': (1, W)})
+    out.update({'final.norm': (W,), 'head': (V, W)})
+    return out
+
+
+def random_dugalix_weights(cfg, seed=0, device='cpu'):
+    """Seeded bf16 tensors for a Dugalix config dict: matrices N(0, 1/fan_in), the embedding of unit spread, norm gains (stored
+    around zero) 0.1 N, biases 0.1 N except the gate biases of the matrix memory (input gates around -1, forget gates around 3 so
+    that the memory reaches back over tens of tokens), per-head score biases around -2 (sigmoid weights add up over the window),
+    shift factors uniform in [0, 1], router rows of a spread that gives peaked probabilities and choice corrections of 0.1 N
+    (comparable to the probabilities, so that they change which experts win)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda s: torch.randn(s, generator=g, device=device, dtype=torch.float32)
+    w = {}
+    for name, shape in dugalix_tensor_shapes(cfg).items():
+        leaf = name.split('.', 1)[1] if name.startswith('l') and name[1].isdigit() else name
+        if leaf.endswith('right.i.b'):
+            t = -1.0 + 0.5 * rn(shape)
+        elif leaf.endswith('right.f.b'):
+            t = 3.0 + rn(shape)
+        elif leaf.endswith('.pb'):
+            t = -2.0 + 0.5 * rn(shape)
+        elif leaf.endswith('.b'):
+            t = 0.1 * rn(shape)
+        elif leaf == 'shift':
+            t = torch.rand(shape, generator=g, device=device, dtype=torch.float32)
+        elif leaf == 'embed':
+            t = rn(shape)
+        elif 'norm' in leaf.rsplit('.', 1)[-1]:
+            t = 0.1 * rn(shape)
+        elif leaf == 'mlp.correction':
+            t = 0.1 * rn(shape)
+        elif leaf == 'mlp.router':
+            t = rn(shape) * (2.0 / shape[1] ** 0.5)
+        else:
+            t = rn(shape) / shape[-1] ** 0.5
+        w[name] = t.to(torch.bfloat16)
+    return w
