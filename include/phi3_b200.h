@@ -512,22 +512,26 @@ int p3_moe_combine_identity(const float* y, int64_t ldy, const int32_t* where, c
  * pre-activations at i_off and f_off (one per head, biases i_bias / f_bias fp32 [heads]).
  *   a = cap tanh(pre_i / cap), b = logsigmoid(cap tanh(pre_f / cap)), m' = max(b + m, a),
  *   S' = e^(b + m - m') S + e^(a - m') k v^T, n' alike with k, y = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6)
- * token by token over the rows of every sequence of `seqs`; y -> out fp32 [T, ld_out], head h at column h * vdim. The state of a
- * slot is `state + slot * p3_matrix_memory_state_floats(...)` floats, read at the start and written at the end of the step. */
+ * token by token over the rows of every sequence of `seqs`. The numerators S'^T q go to out (fp32 [T, ld_out], head h at column
+ * h * vdim), the denominators to den (fp32 [T, n_heads]); p3_headnorm_gate divides. The state of a slot is `state + slot *
+ * p3_matrix_memory_state_floats(...)` floats, read at the start and written at the end of the step. rs_force (0: chosen by the
+ * launch): 2 or 4 = row slices of S per warp with one column per lane, 8 = four slices with two columns; every choice gives the
+ * same numbers. */
 typedef struct {
     const float* proj; int64_t ld_proj; int32_t q_off, k_off, v_off, i_off, f_off;
     const float* i_bias; const float* f_bias;
     int32_t n_heads, dim, vdim; float q_scale, gate_cap;
     float* state; const int32_t* seqs; int32_t n_seqs;
-    float* out; int64_t ld_out;
+    float* out; int64_t ld_out; float* den; int32_t rs_force;
 } p3_matrix_memory_args;
 int64_t p3_matrix_memory_state_floats(int n_heads, int dim, int vdim);
 int p3_matrix_memory_scan(const p3_matrix_memory_args* args, cudaStream_t st);
 
-/* out (act) [T, ldo] = y / sqrt(mean over the head's vdim numbers of y^2 + eps) * gain[c] * sigmoid(gate[t][c]) * scale, y fp32
- * [T, ldy] with n_heads x vdim columns, gate fp32 logits [T, ld_gate] or NULL */
-int p3_headnorm_gate(const float* y, int64_t ldy, int n_heads, int vdim, const float* gain, const float* gate, int64_t ld_gate,
-                     float scale, float eps, void* out, int64_t ldo, int out_f32, int64_t T, cudaStream_t st);
+/* out (act) [T, ldo] = v / sqrt(mean over the head's vdim numbers of v^2 + eps) * gain[c] * sigmoid(gate[t][c]) * scale with
+ * v = y / den[t][head] (den fp32 [T, n_heads] or NULL: v = y), y fp32 [T, ldy] with n_heads x vdim columns, gate fp32 logits
+ * [T, ld_gate] or NULL */
+int p3_headnorm_gate(const float* y, int64_t ldy, const float* den, int n_heads, int vdim, const float* gain, const float* gate,
+                     int64_t ld_gate, float scale, float eps, void* out, int64_t ldo, int out_f32, int64_t T, cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -84,7 +84,7 @@ _SIGS = {
     'p3_relu2': [_p, _l, _p, _l, _p, _l, _i, _l, _i, _p],
     'p3_router_groups': [_p, _l, _p, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p],
     'p3_moe_combine_identity': [_p, _l, _p, _p, _p, _i, _i, _p, _p, _l, _p, _l, _i, _p],
-    'p3_headnorm_gate': [_p, _l, _i, _i, _p, _p, _l, _f, _f, _p, _l, _i, _l, _p],
+    'p3_headnorm_gate': [_p, _l, _p, _i, _i, _p, _p, _l, _f, _f, _p, _l, _i, _l, _p],
 }
 ROUTER_SOFTMAX, ROUTER_GROUP_MAX, ROUTER_PLAIN_WEIGHTS = 1, 2, 4          # mode bits of p3_router_groups
 _STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode', 'p3_latent_post',
@@ -261,4 +261,4 @@ class MatrixMemoryArgs(C.Structure):
     _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('k_off', C.c_int32), ('v_off', C.c_int32),
                 ('i_off', C.c_int32), ('f_off', C.c_int32), ('i_bias', _p), ('f_bias', _p),
                 ('n_heads', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('q_scale', C.c_float), ('gate_cap', C.c_float),
-                ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l)]
+                ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l), ('den', _p), ('rs_force', C.c_int32)]

@@ -216,7 +216,7 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, i
 // ex2); the weights are rounded to bf16 only as the A operand of P.V, taken straight from the score accumulators. K fragments
 // come by ldmatrix from the row-major page, V by ldmatrix.trans. A page that every row of the tile sees in full (behind the
 // diagonal, inside the window) skips the visibility tests.
-template <int DK, int DN, int MINB>
+template <int DK, int DN, int MINB, bool SIG>
 __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
@@ -240,7 +240,9 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
     const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
     const float* pen = a.penalty ? a.penalty + (size_t)h * a.n_penalty : nullptr;
     const int kc = d / 8, vc = dv / 8;                       // 16-byte chunks per row
-    const int pg_lo = first / P3_PAGE, pg_hi = last / P3_PAGE;
+    const PageWalk walk(a, first, last);
+    constexpr bool sig = SIG;                                // sigmoid weights (a.sig_bias): no running maximum, no denominator
+    const float sbias2 = sig ? a.sig_bias[h] * LOG2E : 0.f;
 
     auto stage_page = [&](int pg, int st) {                  // all threads: issue the copies of page pg into stage st
         const int page = bt[pg];
@@ -255,7 +257,7 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
         const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
         pen_s[st * 128 + tid] = (pen && dist >= 0) ? pen[min(dist, a.n_penalty - 1)] * LOG2E : 0.f;
     };
-    stage_page(pg_lo, 0);
+    stage_page(walk.page(0), 0);
     cp_async_commit();
 
     const bf16* q = (const bf16*)a.q + (size_t)h * d;
@@ -276,10 +278,10 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
 #pragma unroll
     for (int n = 0; n < DN; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-    for (int pg = pg_lo; pg <= pg_hi; pg++) {
-        const int st = (pg - pg_lo) & 1;
+    for (int it = 0; it < walk.n; it++) {
+        const int pg = walk.page(it), st = it & 1;
         __syncthreads();                                     // every warp is done with the stage that is refilled now
-        if (pg < pg_hi) stage_page(pg + 1, st ^ 1);
+        if (it + 1 < walk.n) stage_page(walk.page(it + 1), st ^ 1);
         cp_async_commit();
         cp_async_wait<1>();                                  // page pg has landed (this thread's copies) ...
         __syncthreads();                                     // ... and everyone else's
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
         }
         float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
         // every key of the page is visible to every row of the tile: behind the first row, and the last row's window reaches it
-        const bool full = pg * P3_PAGE + 63 <= pos0 && (a.window <= 0 || pos0 + 63 - pg * P3_PAGE < a.window);
+        const bool full = pg * P3_PAGE + 63 <= pos0 && (a.window <= 0 || pos0 + 63 - pg * P3_PAGE < a.window || pg * P3_PAGE + 63 < walk.keep);
         // the penalty depends on row - col only, and this thread's second row is its first plus 8: the penalties of (r1, key block
         // j) are those of (r0, key block j - 1), so 18 values serve the 32 scores
         float pq[9][2];
@@ -328,11 +330,20 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
-                    const int dist = pos0 + row - (pg * P3_PAGE + col);
-                    const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
+                    const int kpos = pg * P3_PAGE + col, dist = pos0 + row - kpos;
+                    const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window || kpos < walk.keep);
                     s[j][e] = vis ? fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]) : -FLT_MAX;
                 }
         }
+        if (sig) {                                           // weight = 1 / (1 + 2^-(score + bias)), 0 for a masked key
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v = s[j][e];
+                    s[j][e] = (full || v > -FLT_MAX) ? __frcp_rn(1.0f + ex2f(-(v + sbias2))) : 0.f;
+                }
+        } else {
         {   // row maxima by a tree (depth 4 instead of a chain of 16)
             float t0[8], t1[8];
 #pragma unroll
@@ -364,6 +375,7 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
 #pragma unroll
             for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
         }
+        }
 #pragma unroll
         for (int t = 0; t < 4; t++) {                        // 16 keys per step
             uint32_t pa[4];
@@ -390,8 +402,8 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
         const int row = half ? r1 : r0;
         if (row >= nq) continue;
         const float l = half ? l1 : l0;
-        const float gate = a.gate ? a.gate[(size_t)(row0 + row) * a.n_heads + h] : 1.f;
-        const float inv = l > 0.f ? gate / l : 0.f;
+        const float gate = (a.gate ? a.gate[(size_t)(row0 + row) * a.n_heads + h] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
+        const float inv = sig ? gate : (l > 0.f ? gate / l : 0.f);
 #pragma unroll
         for (int n = 0; n < DN; n++) {
             const int c = n * 8 + tig * 2;
@@ -615,10 +627,11 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
     const int g = PARTS ? blockIdx.y / v_parts : blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int pg_first = first / P3_PAGE, pg_last = pos / P3_PAGE;
-    const int per = (pg_last - pg_first + n_splits) / n_splits;           // pages per slice, rounded up
-    const int pg_lo = pg_first + split * per, pg_hi = min(pg_last, pg_lo + per - 1);
-    const int n_pg = max(0, pg_hi - pg_lo + 1);
+    const PageWalk walk(a, first, pos);                      // the kept first pages, then the window's pages: one running index
+    const int per = (walk.n + n_splits - 1) / n_splits;      // pages per slice, rounded up
+    const int pg_lo = split * per;                           // first running index of this slice
+    const int n_pg = max(0, min(walk.n, pg_lo + per) - pg_lo);
+    const bool sig = a.sig_bias != nullptr;                  // sigmoid weights: the maximum is pinned at 0, the sum is not used
     const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
     const int kc = d / 8, vc = dv / 8;
     const float scale2 = a.scale * LOG2E;
@@ -642,10 +655,10 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
         };
         __syncthreads();                                     // the merge buffer of the previous pass is read
         for (int s = 0; s < n_stages - 1; s++) {
-            if (s < n_pg) stage_page(pg_lo + s, bt[pg_lo + s], s);
+            if (s < n_pg) stage_page(walk.page(pg_lo + s), bt[walk.page(pg_lo + s)], s);
             cp_async_commit();
         }
-        int next_page = (n_stages - 1 < n_pg) ? bt[pg_lo + n_stages - 1] : 0;
+        int next_page = (n_stages - 1 < n_pg) ? bt[walk.page(pg_lo + n_stages - 1)] : 0;
         const bf16* q = (const bf16*)a.q + (size_t)row * a.ld_q + (size_t)hb * d;
         uint32_t qf[DK][4];
 #pragma unroll
@@ -659,8 +672,9 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
         }
         // the sink enters once per head: as the initial state of slice 0's first warp
         const bool s0 = split == 0 && warp == 0 && a.sink;
-        float m0 = (s0 && gid < nr) ? a.sink[hb + gid] * LOG2E : -FLT_MAX;
-        float m1 = (s0 && gid + 8 < nr) ? a.sink[hb + gid + 8] * LOG2E : -FLT_MAX;
+        float m0 = sig ? 0.f : (s0 && gid < nr) ? a.sink[hb + gid] * LOG2E : -FLT_MAX;
+        float m1 = sig ? 0.f : (s0 && gid + 8 < nr) ? a.sink[hb + gid + 8] * LOG2E : -FLT_MAX;
+        const float sb0 = (sig && gid < nr) ? a.sig_bias[hb + gid] * LOG2E : 0.f, sb1 = (sig && gid + 8 < nr) ? a.sig_bias[hb + gid + 8] * LOG2E : 0.f;
         float l0 = (s0 && gid < nr && tig == 0) ? 1.f : 0.f, l1 = (s0 && gid + 8 < nr && tig == 0) ? 1.f : 0.f;
         const bool has_pen = a.penalty != nullptr;
         const int prow0 = min(gid, nr - 1) * P3_PAGE, prow1 = min(gid + 8, nr - 1) * P3_PAGE;
@@ -672,10 +686,10 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
             cp_async_wait_pending(n_stages - 2);             // page i has landed (this thread's copies) ...
             __syncthreads();                                 // ... and everyone else's; the stage of page i - 1 is free
             const int ahead = i + n_stages - 1;
-            if (ahead < n_pg) stage_page(pg_lo + ahead, next_page, ahead % n_stages);
+            if (ahead < n_pg) stage_page(walk.page(pg_lo + ahead), next_page, ahead % n_stages);
             cp_async_commit();
-            if (ahead + 1 < n_pg) next_page = bt[pg_lo + ahead + 1];
-            const int pg = pg_lo + i;
+            if (ahead + 1 < n_pg) next_page = bt[walk.page(pg_lo + ahead + 1)];
+            const int pg = walk.page(pg_lo + i);
             const bf16* Ks = reinterpret_cast<const bf16*>(smraw + (size_t)(i % n_stages) * stage_bytes);
             const bf16* Vs = Ks + P3_PAGE * ldk;
             const float* Ps = reinterpret_cast<const float*>(Vs + P3_PAGE * ldv);
@@ -699,7 +713,7 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
                 for (int e = 0; e < 4; e++) {
                     const int col = warp * 16 + j * 8 + tig * 2 + (e & 1);
                     const int kpos = pg * P3_PAGE + col, dist = pos - kpos;
-                    const bool vis = kpos >= first && dist >= 0 && ((e < 2) ? gid : gid + 8) < nr;
+                    const bool vis = (kpos >= first || kpos < walk.keep) && dist >= 0 && ((e < 2) ? gid : gid + 8) < nr;
                     float v = -FLT_MAX;
                     if (vis) v = fmaf(s[j][e], scale2, has_pen ? -LOG2E * Ps[((e < 2) ? prow0 : prow1) + col] : 0.f);
                     s[j][e] = v;
@@ -707,7 +721,7 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
                 }
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            const float n0 = sig ? 0.f : fmaxf(m0, mx0), n1 = sig ? 0.f : fmaxf(m1, mx1);
             const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);
             m0 = n0; m1 = n1;
             float ps0 = 0.f, ps1 = 0.f;
@@ -716,7 +730,7 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const float v = s[j][e];
-                    const float p = v > -FLT_MAX ? exp2f(v - ((e < 2) ? n0 : n1)) : 0.f;
+                    const float p = v <= -FLT_MAX ? 0.f : sig ? 1.0f / (1.0f + exp2f(-(v + ((e < 2) ? sb0 : sb1)))) : exp2f(v - ((e < 2) ? n0 : n1));
                     s[j][e] = p;
                     if (e < 2) ps0 += p; else ps1 += p;
                 }
@@ -771,8 +785,8 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
                 acc = fmaf(Os[(size_t)(w * 16 + r) * dv + c], f, acc);
             }
             if (n_splits == 1) {
-                const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
-                ((bf16*)a.out)[(size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c] = __float2bfloat16_rn(L > 0.f ? acc * gate / L : 0.f);
+                const float gate = (a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
+                ((bf16*)a.out)[(size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c] = __float2bfloat16_rn(L > 0.f ? acc * gate / (sig ? 1.f : L) : 0.f);
             } else {
                 float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (a.vdim + 2);
                 if (c == 0 && vc0 == 0) { w[0] = M; w[1] = L; }            // every column block forms the same maximum and sum
@@ -866,7 +880,7 @@ int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
 static bool prefill_mma_ok(const p3_attn_window_args* a) {
     static int off = -1;
     if (off < 0) { const char* e = getenv("P3_ATTN_WINDOW_MMA"); off = (e && e[0] == '0') ? 1 : 0; }
-    return !off && !a->keep_first && !a->sig_bias && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 256 && a->vdim <= 256 &&
+    return !off && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 256 && a->vdim <= 256 &&
            a->ld_q % 2 == 0 && a->ld_out % 2 == 0 && ((uintptr_t)a->q & 3) == 0 && ((uintptr_t)a->out & 3) == 0 &&
            ((uintptr_t)a->k_pool & 15) == 0 && ((uintptr_t)a->v_pool & 15) == 0 && a->v_ld % 8 == 0;
 }
@@ -877,16 +891,18 @@ static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
     const int vcols = wide ? 128 : (a->dim <= 64 && a->vdim <= 64 ? 64 : 128), dvs = a->vdim < vcols ? a->vdim : vcols;
     const size_t bytes = 2 * (sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + dvs + 8) + 128 * sizeof(float));   // two stages
     const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads, (unsigned)((a->vdim + vcols - 1) / vcols));
-    if (wide) {
-        if (set_smem(attn_window_prefill_mma_kernel<16, 16, 2>, bytes, "attn_window_prefill")) return -1;
-        p3_launch_pdl(attn_window_prefill_mma_kernel<16, 16, 2>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
-    } else if (a->dim <= 64 && a->vdim <= 64) {
-        if (set_smem(attn_window_prefill_mma_kernel<4, 8, 3>, bytes, "attn_window_prefill")) return -1;
-        p3_launch_pdl(attn_window_prefill_mma_kernel<4, 8, 3>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
-    } else {
-        if (set_smem(attn_window_prefill_mma_kernel<8, 16, 3>, bytes, "attn_window_prefill")) return -1;
-        p3_launch_pdl(attn_window_prefill_mma_kernel<8, 16, 3>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
-    }
+#define GO(DK, DN, MINB)                                                                                        \
+    do { if (a->sig_bias) {                                                                                      \
+             if (set_smem(attn_window_prefill_mma_kernel<DK, DN, MINB, true>, bytes, "attn_window_prefill")) return -1;       \
+             p3_launch_pdl(attn_window_prefill_mma_kernel<DK, DN, MINB, true>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);   \
+         } else {                                                                                                \
+             if (set_smem(attn_window_prefill_mma_kernel<DK, DN, MINB, false>, bytes, "attn_window_prefill")) return -1;      \
+             p3_launch_pdl(attn_window_prefill_mma_kernel<DK, DN, MINB, false>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);  \
+         } } while (0)
+    if (wide) GO(16, 16, 2);
+    else if (a->dim <= 64 && a->vdim <= 64) GO(4, 8, 3);
+    else GO(8, 16, 3);
+#undef GO
     return 0;
 }
 

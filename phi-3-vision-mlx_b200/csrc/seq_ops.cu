@@ -766,6 +766,52 @@ __global__ void relu2_kernel(const float* __restrict__ u, int64_t ld, const floa
     }
 }
 
+// four columns per thread (F, the row pitches and the pointers are multiples of four elements): 16-byte loads
+template <typename AT>
+__global__ void relu2_vec4_kernel(const float* __restrict__ u, int64_t ld, const float* __restrict__ row_gate, int64_t ld_gate,
+                                  AT* __restrict__ out, int64_t ldo, int64_t R, int F) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int F4 = F / 4;
+    const int64_t n = R * F4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F4; const int c = (int)(i % F4) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(u + (size_t)r * ld + c);
+        const float g = row_gate ? 1.0f / (1.0f + expf(-row_gate[r * ld_gate])) : 1.f;
+        const float a = fmaxf(v.x, 0.f), b = fmaxf(v.y, 0.f), e = fmaxf(v.z, 0.f), f = fmaxf(v.w, 0.f);
+        AT* o = out + (size_t)r * ldo + c;
+        if constexpr (sizeof(AT) == 4) *reinterpret_cast<float4*>(o) = make_float4(a * a * g, b * b * g, e * e * g, f * f * g);
+        else *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(a * a * g, b * b * g), pack_bf16(e * e * g, f * f * g));
+    }
+}
+
+// token shift, four channels per thread (W a multiple of four, 16-byte aligned rows)
+template <typename AT>
+__global__ void token_shift_vec4_kernel(const float* __restrict__ h, const float* __restrict__ shift, float* state,
+                                        const int32_t* __restrict__ seqs, const int32_t* __restrict__ slot_seq,
+                                        const int32_t* __restrict__ tok_slot, AT* __restrict__ out, int W) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int64_t t = blockIdx.x;
+    const int slot = tok_slot[t];
+    const int4 rec = reinterpret_cast<const int4*>(seqs)[slot_seq[slot]];   // {first row, rows, slot, first position}
+    const bool first = t == rec.x;
+    float* sv = state + (size_t)slot * W;
+    const float* hr = h + (size_t)t * W;
+    const float* prev = first ? (rec.w > 0 ? sv : nullptr) : hr - W;
+    const float* lastr = h + (size_t)(rec.x + rec.y - 1) * W;
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+        const float4 hv = *reinterpret_cast<const float4*>(hr + i), sh = *reinterpret_cast<const float4*>(shift + i);
+        const float4 pv = prev ? *reinterpret_cast<const float4*>(prev + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float y0 = hv.x + (pv.x - hv.x) * sh.x, y1 = hv.y + (pv.y - hv.y) * sh.y;
+        const float y2 = hv.z + (pv.z - hv.z) * sh.z, y3 = hv.w + (pv.w - hv.w) * sh.w;
+        AT* o = out + (size_t)t * W + i;
+        if constexpr (sizeof(AT) == 4) *reinterpret_cast<float4*>(o) = make_float4(y0, y1, y2, y3);
+        else *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(y0, y1), pack_bf16(y2, y3));
+        if (first) *reinterpret_cast<float4*>(sv + i) = *reinterpret_cast<const float4*>(lastr + i);
+    }
+}
+
 // ---------------------------------------------------------------- weighted sum of the chosen experts, identity experts and an addend
 __global__ void moe_combine_identity_kernel(const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ where,
                                             const int32_t* __restrict__ ids, const float* __restrict__ wts, int top, int n_real,
@@ -1005,6 +1051,12 @@ extern "C" int p3_token_shift(const float* h, const float* shift, float* state, 
     P3_CHECK_ARG(((uintptr_t)seqs & 15) == 0, "token_shift: the sequence records must be 16-byte aligned");
     if (T == 0) return 0;
     const int th = W >= 2048 ? 256 : 128;
+    if (W % 4 == 0 && (((uintptr_t)h | (uintptr_t)shift | (uintptr_t)state | (uintptr_t)out) & 15) == 0) {
+        if (out_f32) p3_launch_pdl(token_shift_vec4_kernel<float>, dim3((unsigned)T), dim3(th), (size_t)(0), st, h, shift, state, seqs, slot_seq, tok_slot, (float*)out, W);
+        else p3_launch_pdl(token_shift_vec4_kernel<bf16>, dim3((unsigned)T), dim3(th), (size_t)(0), st, h, shift, state, seqs, slot_seq, tok_slot, (bf16*)out, W);
+        P3_CHECK_LAUNCH("token_shift");
+        return 0;
+    }
     if (out_f32) p3_launch_pdl(token_shift_kernel<float>, dim3((unsigned)T), dim3(th), (size_t)(0), st, h, shift, state, seqs, slot_seq, tok_slot, (float*)out, W);
     else p3_launch_pdl(token_shift_kernel<bf16>, dim3((unsigned)T), dim3(th), (size_t)(0), st, h, shift, state, seqs, slot_seq, tok_slot, (bf16*)out, W);
     P3_CHECK_LAUNCH("token_shift");
@@ -1029,6 +1081,14 @@ extern "C" int p3_qkv_rope_post(const p3_qkv_rope_post_args* a, cudaStream_t st)
 extern "C" int p3_relu2(const float* u, int64_t ld, const float* row_gate, int64_t ld_gate, void* out, int64_t ldo, int out_f32,
                         int64_t R, int F, cudaStream_t st) {
     if (R == 0 || F == 0) return 0;
+    if (F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && (((uintptr_t)u | (uintptr_t)out) & 15) == 0) {
+        const int64_t n4 = R * (F / 4);
+        const unsigned g4 = (unsigned)((n4 + 255) / 256 < 148 * 16 ? (n4 + 255) / 256 : 148 * 16);
+        if (out_f32) p3_launch_pdl(relu2_vec4_kernel<float>, dim3(g4), dim3(256), (size_t)(0), st, u, ld, row_gate, ld_gate, (float*)out, ldo, R, F);
+        else p3_launch_pdl(relu2_vec4_kernel<bf16>, dim3(g4), dim3(256), (size_t)(0), st, u, ld, row_gate, ld_gate, (bf16*)out, ldo, R, F);
+        P3_CHECK_LAUNCH("relu2");
+        return 0;
+    }
     const int64_t n = R * F;
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     if (out_f32) p3_launch_pdl(relu2_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, u, ld, row_gate, ld_gate, (float*)out, ldo, R, F);

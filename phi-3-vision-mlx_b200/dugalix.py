@@ -58,7 +58,7 @@ class DugalixB200(PagedLM):
         mat = lambda t: t.to(self.dev, dtype).contiguous()                     # matrices: the compute type
         f32 = lambda t: t.to(self.dev, torch.float32).contiguous()            # everything that enters fp32 arithmetic
         gain = lambda t, k=1.0: ((1.0 + t.to(self.dev, torch.float32)) * k).contiguous()   # weights stored around zero
-        pad16 = lambda parts: parts + ([torch.zeros(-sum(p.shape[0] for p in parts) % 16, W, dtype=parts[0].dtype)]
+        pad16 = lambda parts: parts + ([torch.zeros(-sum(p.shape[0] for p in parts) % 16, W, dtype=parts[0].dtype, device=parts[0].device)]
                                        if sum(p.shape[0] for p in parts) % 16 else [])
 
         def expect(name, shape):
@@ -100,8 +100,8 @@ class DugalixB200(PagedLM):
                 out_parts.append(w[b + 'o'])
             # all input projections of the layer are one product (rows padded to a multiple of 16 so that small batches keep the
             # weight-streaming kernel); the output projections of both halves read one concatenated activation row
-            L['in_w'] = mat(torch.cat(pad16([t.cpu() for t in parts]), 0))
-            L['out_w'] = mat(torch.cat([t.cpu() for t in out_parts], 1))
+            L['in_w'] = mat(torch.cat(pad16(parts), 0))
+            L['out_w'] = mat(torch.cat(out_parts, 1))
             L['freq'] = (torch.tensor(rot_frequencies(at.rot), dtype=torch.float64).to(self.dev, torch.float32)
                          if at.rot is not None else None)
             L['rot_n'] = at.rot.dims if at.rot is not None else 0
@@ -118,7 +118,7 @@ class DugalixB200(PagedLM):
                     expect(q + 'router', (f.outputs, W))
                     parts2 = ([w[q + 'shared.up'], w[q + 'shared.sg']] if sff else []) + [w[q + 'router']]
                     L['sg_off'], L['r_off'] = sff, sff + (1 if sff else 0)
-                    L['in2_w'] = mat(torch.cat(pad16([t.cpu() for t in parts2]), 0))
+                    L['in2_w'] = mat(torch.cat(pad16(parts2), 0))
                     L['sh_down'] = mat(w[q + 'shared.down']) if sff else None
                     if f.experts:
                         L['up'] = mat(torch.stack([w[f'{q}e{e}.up'] for e in range(f.experts)], 0))
@@ -174,8 +174,9 @@ class DugalixB200(PagedLM):
             ha = h32 if self.f32 else torch.empty((T, self.W), dtype=self.dtype, device=self.dev)
         else:
             h32, ha = None, torch.empty((T, self.W), dtype=self.dtype, device=self.dev)
-        call('p3_postnorm_prenorm', ptr(y), y.stride(0) if y is not None else 0, ptr(y_bias), ptr(post), ptr(x), ptr(pre), ptr(h32),
-             None if self.f32 else ptr(ha), self.f32, T, self.W, self.eps, _stream())
+        nb = T * self.W * ((12 if y is not None else 4) + (0 if pre is None else (4 if h32 is not None else 0) + (0 if self.f32 else 2)))
+        self.rows('norm', nb, 'p3_postnorm_prenorm', ptr(y), y.stride(0) if y is not None else 0, ptr(y_bias), ptr(post), ptr(x),
+                  ptr(pre), ptr(h32), None if self.f32 else ptr(ha), self.f32, T, self.W, self.eps, _stream())
         return h32, ha
 
     def forward(self, b, pool, trace=None):
@@ -217,8 +218,8 @@ class DugalixB200(PagedLM):
         at, mem = m.att, m.mem
         H, G, d, dv = at.heads, at.kv_heads, at.dim, at.vdim
         u = e(T, W, dt=act)
-        call('p3_token_shift', ptr(h32), ptr(L['shift']), ptr(pool.state[L['shift_state']]), ptr(b.seqs), ptr(b.slot_seq),
-             ptr(b.tok_slot), ptr(u), self.f32, T, W, st)
+        self.rows('shift', T * W * (4 + (4 if self.f32 else 2)), 'p3_token_shift', ptr(h32), ptr(L['shift']),
+                  ptr(pool.state[L['shift_state']]), ptr(b.seqs), ptr(b.slot_seq), ptr(b.tok_slot), ptr(u), self.f32, T, W, st)
         proj = e(T, L['in_w'].shape[0])
         self.linear(u, L['in_w'], proj, nxt=L['out_w'])
         n_att = H * dv
@@ -231,7 +232,8 @@ class DugalixB200(PagedLM):
         a.k_pool, a.v_pool = ptr(pool.k[li]), ptr(pool.v[li])
         a.block_table, a.bt_stride = ptr(pool.block_table), pool.block_table.stride(0)
         a.tok_slot, a.tok_pos, a.T, a.act_f32, a.cache_f32 = ptr(b.tok_slot), ptr(b.tok_pos), T, self.f32, self.f32
-        call_struct('p3_qkv_rope_post', a, st)
+        esz = 4 if self.f32 else 2
+        self.rows('qkv_post', T * ((H + G) * d + max(0, G * dv)) * (4 + esz), 'p3_qkv_rope_post', a)
         w = _lib.AttnWindowArgs()
         w.q, w.ld_q, w.k_pool, w.v_pool = ptr(q), q.stride(0), ptr(pool.k[li]), ptr(pool.v[li])
         w.block_table, w.bt_stride = ptr(pool.block_table), pool.block_table.stride(0)
@@ -239,7 +241,6 @@ class DugalixB200(PagedLM):
         w.n_heads, w.n_kv, w.dim, w.vdim, w.scale, w.window, w.keep_first = H, G, d, dv, at.scale, at.window, at.keep_first
         w.sig_bias, w.out_scale = ptr(L['pb']), m.att_scale
         w.act_f32, w.cache_f32 = self.f32, self.f32
-        esz = 4 if self.f32 else 2
         seen = lambda n: (min(at.window, n) + min(at.keep_first, max(0, n - at.window))) if at.window else n   # keys a query at n - 1 sees
         if b.n_pf:
             w.tiles, w.n_tiles = ptr(b.pf_tiles), b.n_pf
@@ -269,12 +270,13 @@ class DugalixB200(PagedLM):
             r.i_bias, r.f_bias, r.n_heads, r.dim, r.vdim = ptr(L['mi_b']), ptr(L['mf_b']), Hm, dm, dvm
             r.q_scale, r.gate_cap = dm ** -0.5, mem.gate_cap
             r.state, r.seqs, r.n_seqs = ptr(pool.state[L['mem_state']]), ptr(b.seqs), b.n_seq
-            r.out, r.ld_out = ptr(ym), ym.stride(0)
+            den = e(T, Hm)
+            r.out, r.ld_out, r.den = ptr(ym), ym.stride(0), ptr(den)
             ev = self._ev()
             call_struct('p3_matrix_memory_scan', r, st)
             self._ev(ev, 'memory_scan', 4 * T * Hm * dm * dvm, T * L['in_w'].shape[0] * 4)
-            call('p3_headnorm_gate', ptr(ym), ym.stride(0), Hm, dvm, ptr(L['m_gain']), ptr(proj[:, L['mg_off']:]), proj.stride(0),
-                 m.mem_scale, self.eps, ptr(cat[:, n_att:]), cat.stride(0), self.f32, T, st)
+            self.rows('headnorm', T * Hm * dvm * (8 + esz), 'p3_headnorm_gate', ptr(ym), ym.stride(0), ptr(den), Hm, dvm, ptr(L['m_gain']),
+                      ptr(proj[:, L['mg_off']:]), proj.stride(0), m.mem_scale, self.eps, ptr(cat[:, n_att:]), cat.stride(0), self.f32, T, st)
         y = e(T, W)
         f = L['cfg'].ff
         after = L.get('up') if f is not None and f.kind == 'dense' else (L.get('in2_w') if f is not None else None)
@@ -287,7 +289,8 @@ class DugalixB200(PagedLM):
         hid = torch.empty((T, f.ff), dtype=self.dtype, device=self.dev)
         y = torch.empty((T, self.W), dtype=torch.float32, device=self.dev)
         self.linear(h, L['up'], up, nxt=L['down'])
-        call('p3_relu2', ptr(up), up.stride(0), None, 0, ptr(hid), hid.stride(0), self.f32, T, f.ff, st)
+        self.rows('activation', T * f.ff * (4 + (4 if self.f32 else 2)), 'p3_relu2', ptr(up), up.stride(0), None, 0, ptr(hid),
+                  hid.stride(0), self.f32, T, f.ff, st)
         self.linear(hid, L['down'], y)
         return y
 

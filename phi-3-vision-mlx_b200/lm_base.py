@@ -60,6 +60,16 @@ class PagedLM:
             self.profile.append((kind, start, e, flops, nbytes))
         return e
 
+    def rows(self, kind, nbytes, name, *args):
+        """a row kernel (norms, rotations, activations, routing) launched through _lib.call, or through _lib.call_struct when
+        `args` is (argument struct,); bench.py's instrumentation times it under `kind` with the bytes it moves"""
+        ev = self._ev()
+        if len(args) == 1 and hasattr(args[0], '_fields_'):
+            call_struct(name, args[0], _stream())
+        else:
+            call(name, *args)
+        self._ev(ev, kind, 0, nbytes)
+
     # ------------------------------------------------------------------ matrix products
     def linear(self, x, w, out, bias32=None, bias16=None, nxt=None):
         """out[M,N] (fp32 or act type, by out.dtype) = x[M,K] w[N,K]^T (+ bias). Returns the bias (fp32) that is STILL TO ADD: None

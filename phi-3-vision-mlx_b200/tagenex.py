@@ -131,7 +131,7 @@ class TagenexB200(PagedLM):
             a.k_pool, a.v_pool = ptr(pool.k[li]), ptr(pool.v[li])
             a.block_table, a.bt_stride = ptr(pool.block_table), pool.block_table.stride(0)
             a.tok_slot, a.tok_pos, a.T, a.act_f32, a.cache_f32 = ptr(b.tok_slot), ptr(b.tok_pos), T, self.f32, self.f32
-            call_struct('p3_qkv_post', a, st)
+            self.rows('qkv_post', T * (proj.shape[1] * 4 + (nq + nk + nv) * (4 if self.f32 else 2)), 'p3_qkv_post', a)
             w = _lib.AttnWindowArgs()
             w.q, w.ld_q, w.k_pool, w.v_pool = ptr(q), q.stride(0), ptr(pool.k[li]), ptr(pool.v[li])
             w.block_table, w.bt_stride = ptr(pool.block_table), pool.block_table.stride(0)
@@ -163,20 +163,21 @@ class TagenexB200(PagedLM):
             f = L['cfg'].ff
             after = self.layers[li + 1]['qkvg'] if li + 1 < len(self.layers) else self.head
             self.linear(att, L['o'], y, nxt=L['gu'] if f is not None and f.kind == 'dense' else (after if f is None else None))
-            call('p3_postnorm_residual', ptr(y), y.stride(0), None, ptr(L['norm1']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
+            self.rows('norm', T * W * (12 + (4 if self.f32 else 2)), 'p3_postnorm_residual', ptr(y), y.stride(0), None, ptr(L['norm1']),
+                      ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
             f = L['cfg'].ff
             if f is not None:
                 if f.kind == 'dense':
                     gu, hid = e(T, 2 * f.ff), e(T, f.ff, dt=act)
                     left = self.linear(xa, L['gu'], gu, L['gu_b32'], L['gu_b16'], nxt=L['down'])
-                    call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, T, f.ff, f.limit,
-                         TagenexConfig.GLU_ALPHA, ptr(left), st)
+                    self.rows('activation', T * f.ff * (8 + (4 if self.f32 else 2)), 'p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid),
+                              hid.stride(0), self.f32, T, f.ff, f.limit, TagenexConfig.GLU_ALPHA, ptr(left), st)
                     left = self.linear(hid, L['down'], y, L['down_b32'], L['down_b16'], nxt=after)
                 else:
                     self._moe(L, f, xa, y, T)
                     left = None
-                call('p3_postnorm_residual', ptr(y), y.stride(0), ptr(left), ptr(L['norm2']), ptr(x), ptr(xa), self.f32, T, W,
-                     self.eps, st)
+                self.rows('norm', T * W * (12 + (4 if self.f32 else 2)), 'p3_postnorm_residual', ptr(y), y.stride(0), ptr(left),
+                          ptr(L['norm2']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
             if trace is not None:
                 trace.append(x.clone())
         if not b.R:
