@@ -508,7 +508,9 @@ def _engine_model_numbers(m, B, L, CTX_D, NEW_D, vocab, args, hbm, tf):
         f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
     m.profile = None
     kern_pf = {k: dict(ms=round(v[0], 3), launches=v[3], tflops=round(v[1] / v[0] / 1e9, 1),
-                       frac_of_measured_bf16=round(v[1] / v[0] / 1e9 / tf, 3)) for k, v in fam.items()}
+                       frac_of_measured_bf16=round(v[1] / v[0] / 1e9 / tf, 3),
+                       **({'gbs': round(v[2] / v[0] / 1e6, 1), 'frac_of_measured_hbm': round(v[2] / v[0] / 1e6 / hbm, 3)}
+                          if v[2] and not v[1] else {})) for k, v in fam.items()}
     # decode: B sequences at CTX_D tokens of context, one token each per step
     eng.step([(i, prompts[i][:CTX_D - NEW_D - 8], []) for i in range(B)])
     tok = [1] * B
@@ -694,6 +696,71 @@ def run_tapalix(args):
           'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
 
 
+# ------------------------------------------------------------------------------------------------ --arch dugalix
+def _dugalix_cfg(width, heads, kv, dim, window, keep, mh, mdim, mvdim, ff, eff, experts, identity, top, shared, layers, vocab):
+    rot = lambda dims, factor=None: {'base': 500000.0, 'dims': dims, **({'scaling': {'factor': factor}} if factor else {})}
+    par = {'type': 'parallel',
+           'mixer': {'left': {'heads': heads, 'kv_heads': kv, 'dim': dim, 'vdim': dim, 'scale': dim ** -0.5,
+                              'mask': {'size': window, 'keep_first': keep}, 'rot': rot(dim, 4.0)},
+                     'right': {'heads': mh, 'dim': mdim, 'vdim': mvdim, 'gate_cap': 15.0}, 'left_scale': 0.7, 'right_scale': 0.7}}
+    sig = {'type': 'attention', 'mixer': {'heads': heads, 'kv_heads': kv, 'dim': dim, 'vdim': dim, 'scale': dim ** -0.5,
+                                          'mask': {'size': window}, 'rot': rot(dim // 2)}}
+    dense = {'kind': 'dense', 'ff': ff}
+    moe = {'kind': 'moe', 'expert': {'ff': eff}, 'router': {'experts': experts, 'identity': identity, 'top': top,
+                                                              'groups': {'count': 4, 'keep': 2}}, 'shared': {'ff': shared}}
+    return {'architecture': 'Dugalix', 'vocab': vocab, 'width': width, 'norm': {'eps': 1e-5}, 'residual_mult': 0.6,
+            'layers': [dict(sig if i % 2 else par, mlp=(moe if i else dense)) for i in range(layers)]}
+
+
+def run_dugalix(args):
+    """Throughput of the Dugalix design on the continuous-batching engine at layer sizes of a real model (random weights, bf16
+    serving mode), beside Tagenex, the closest existing model (same engine, page pool, product kernels, windowed attention and
+    expert path), at equal width, depth, attention shape, window and expert sizes. One JSON line: per size the prefill and decode
+    tok/s of both and, per kernel family, time and achieved FLOP/s (prefill) or bytes/s (decode) against the measured peaks."""
+    import torch
+    import phi3_b200  # noqa: F401
+    from phi3_b200 import weights
+    from phi3_b200.tagenex import TagenexB200
+    from phi3_b200.dugalix import DugalixB200
+    hbm, _ = peaks()
+    tf = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json'))).get('bf16_tflops', 1590.0) if os.path.exists(
+        os.path.join(ROOT, 'MEASURED_PEAKS.json')) else 1590.0
+    dev = torch.device('cuda:0')
+    sizes = [dict(name='w2048_h16x128_kv4_m8x128x256_e8x1408_L4', width=2048, heads=16, kv=4, dim=128, window=1024, keep=64, mh=8,
+                  mdim=128, mvdim=256, ff=8192, eff=1408, experts=8, identity=8, top=2, shared=2816, layers=4),
+             dict(name='w2048_h16x128_kv4_m8x128x256_e8x1408_L4_b16', width=2048, heads=16, kv=4, dim=128, window=1024, keep=64, mh=8,
+                  mdim=128, mvdim=256, ff=8192, eff=1408, experts=8, identity=8, top=2, shared=2816, layers=4, batch=16),
+             dict(name='w3072_h32x64_kv8_m12x64x256_e12x1024_L4', width=3072, heads=32, kv=8, dim=64, window=512, keep=128, mh=12,
+                  mdim=64, mvdim=256, ff=8192, eff=1024, experts=12, identity=4, top=4, shared=2048, layers=4)]
+    if getattr(args, 'sizes', None):
+        sizes = [sz for i, sz in enumerate(sizes) if str(i) in args.sizes.split(',')]
+    vocab, L, CTX_D, NEW_D = 32064, 2048, 2048, 32
+    out = []
+    for sz in sizes:
+        B = sz.get('batch', 4)
+        cfg = _dugalix_cfg(sz['width'], sz['heads'], sz['kv'], sz['dim'], sz['window'], sz['keep'], sz['mh'], sz['mdim'], sz['mvdim'],
+                           sz['ff'], sz['eff'], sz['experts'], sz['identity'], sz['top'], sz['shared'], sz['layers'], vocab)
+        m = DugalixB200(cfg, weights.random_dugalix_weights(cfg, 0, device=dev), dtype=torch.bfloat16)
+        _, nums = _engine_model_numbers(m, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+        row = dict(size=sz['name'], batch=B, prompt=L, dugalix=nums)
+        del m
+        torch.cuda.empty_cache()
+        # Tagenex at equal size: the same attention shape and window in every layer, the same dense unit and experts (gated there)
+        att = {'type': 'attention', 'mixer': {'heads': sz['heads'], 'kv_heads': sz['kv'], 'dim': sz['dim'], 'vdim': sz['dim'],
+                                              'scale': sz['dim'] ** -0.5, 'v_mix': False, 'mask': {'size': sz['window']}}}
+        dense = {'kind': 'dense', 'ff': sz['ff'], 'limit': 7.0}
+        mix = {'kind': 'moe', 'expert': {'ff': sz['eff'], 'limit': 7.0}, 'router': {'experts': sz['experts'], 'top': sz['top']}}
+        tcfg = {'architecture': 'Tagenex', 'vocab': vocab, 'width': sz['width'], 'norm': {'eps': 1e-5},
+                'layers': [dict(att, mlp=(mix if i else dense)) for i in range(sz['layers'])]}
+        tm = TagenexB200(tcfg, weights.random_tagenex_weights(tcfg, 0, device=dev), dtype=torch.bfloat16)
+        _, row['tagenex_equal_size'] = _engine_model_numbers(tm, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+        del tm
+        torch.cuda.empty_cache()
+        out.append(row)
+    _emit({"metric": "dugalix_prefill_decode_tok_per_s", 'arch': 'dugalix', 'dtype': 'bf16', 'data': 'synthetic', 'n_gpus': 1,
+          'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -701,9 +768,10 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex', 'tapalix'],
-                    help='phi3: the headline workload (default); tagenex / tapalix: prefill / decode throughput of that design on '
-                         'the continuous-batching engine, beside the closest existing model at equal size')
+    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex', 'tapalix', 'dugalix'],
+                    help='phi3: the headline workload (default); tagenex / tapalix / dugalix: prefill / decode throughput of that '
+                         'design on the continuous-batching engine, beside the closest existing model at equal size')
+    ap.add_argument('--sizes', default='', help='with --arch dugalix: indices of the sizes to run, with commas (default: all)')
     args = ap.parse_args()
     if not (args.gpus > 1 and int(os.environ.get('WORLD_SIZE', 1)) == 1):      # the self-launching parent just relays its child
         _claim_stdout()
@@ -713,6 +781,8 @@ def main():
         return run_tagenex(args)
     if args.arch == 'tapalix':
         return run_tapalix(args)
+    if args.arch == 'dugalix':
+        return run_dugalix(args)
     world = int(os.environ.get('WORLD_SIZE', 1))
     if args.gpus > 1 and world == 1:
         # convenience: self-launch under torchrun when called directly with --gpus N
