@@ -507,7 +507,8 @@ int p3_moe_combine_identity(const float* y, int64_t ldy, const int32_t* where, c
                             int n_real, const float* h, const float* add, int64_t ld_add, float* out, int64_t T, int W,
                             cudaStream_t st);
 
-/* Matrix-memory recurrence (csrc/recurrent.cu). Per head: memory S [dim][vdim], normaliser n [dim], stabiliser m (0 at the start).
+/* Matrix-memory recurrence (csrc/recurrent.cu). Per head: memory S [dim][vdim] (dim <= 512), normaliser n [dim], stabiliser m (0 at
+ * the start).
  * From proj (fp32 [T, ld_proj]): q at q_off (times q_scale), k at k_off (heads x dim), v at v_off (heads x vdim), gate
  * pre-activations at i_off and f_off (one per head, biases i_bias / f_bias fp32 [heads]).
  *   a = cap tanh(pre_i / cap), b = logsigmoid(cap tanh(pre_f / cap)), m' = max(b + m, a),

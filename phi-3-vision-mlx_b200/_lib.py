@@ -97,7 +97,8 @@ launches = 0          # number of p3_* kernel-launching calls issued (bench.py r
 
 def exported_symbols():
     return sorted(list(_SIGS) + ['p3_last_error', 'p3_version', 'p3_attention_decode_workspace', 'p3_decode_mega',
-                                 'p3_decode_mega_ctas', 'p3_gemm_fused', 'p3_gemm_plan_weights', 'p3_gemm_skinny_x', 'p3_trace_set', 'p3_trace_count']
+                                 'p3_decode_mega_ctas', 'p3_gemm_fused', 'p3_gemm_plan_weights', 'p3_gemm_skinny_x', 'p3_trace_set', 'p3_trace_count',
+                                 'p3_attn_window_tile_rows', 'p3_matrix_memory_state_floats']
                   + _STRUCT_ENTRIES)
 
 

@@ -308,8 +308,8 @@ class DugalixConfig:
                 r = m['right']
                 mem = SimpleNamespace(heads=int(r['heads']), dim=int(r['dim']), vdim=int(r.get('vdim', r['dim'])),
                                       gate_cap=float(r['gate_cap']))
-                if not 1 <= mem.dim <= 256:
-                    raise NotImplementedError(f'layer {i}: matrix-memory key size {mem.dim}; the kernels take 1 .. 256')
+                if not 1 <= mem.dim <= 512:
+                    raise NotImplementedError(f'layer {i}: matrix-memory key size {mem.dim}; the kernels take 1 .. 512')
                 mixer = SimpleNamespace(kind=kind, att=self._attention(i, m['left'], 'softmax'), mem=mem,
                                         att_scale=float(m.get('left_scale', 1.0)), mem_scale=float(m.get('right_scale', 1.0)))
             else:

@@ -34,7 +34,7 @@ template <typename T> __device__ __forceinline__ void stv(T* p, float v);
 template <> __device__ __forceinline__ void stv<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stv<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-constexpr int MM_TB = 32;        // tokens staged per round
+constexpr int MM_TB = 32;        // tokens staged per round (16 for rows above 256 numbers, so that two rounds fit shared memory)
 constexpr int MM_MAIN = 4;       // warps that own columns of S; one more warp for the gates, one for the normaliser
 constexpr int MM_WARPS = MM_MAIN + 2;
 
@@ -51,7 +51,7 @@ __device__ __forceinline__ void cp_async4z(uint32_t dst, const void* src, int sr
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 
-template <int DS, int RS, int NC>
+template <int DS, int RS, int NC, int TB>
 __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_matrix_memory_args a) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
@@ -61,11 +61,11 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
     // a staged q / k row keeps its RS slices 4 floats apart (pitch DPP): the 16-byte reads of a warp's slices then fall into
     // different banks and one read serves all of them
     constexpr int DPP = DP + 4 * RS;
-    constexpr int ROUND = MM_TB * (2 * DPP + COLS + 3);      // floats of one staged round
+    constexpr int ROUND = TB * (2 * DPP + COLS + 3);      // floats of one staged round
     auto at_row = [](int c) { return c + 4 * (c / DS); };    // where number c of a row lives
     extern __shared__ __align__(16) float sm[];
     const int d = a.dim, dv = a.vdim, H = a.n_heads;
-    // two rounds in flight: [q [MM_TB][DP] (zeros beyond dim) | k alike | v [MM_TB][COLS] | e^(a - m) | e^(b + m' - m) | e^(-m)]
+    // two rounds in flight: [q [TB][DP] (zeros beyond dim) | k alike | v [TB][COLS] | e^(a - m) | e^(b + m' - m) | e^(-m)]
     const int4 rec = reinterpret_cast<const int4*>(a.seqs)[blockIdx.x];
     const int row0 = rec.x, n_tok = rec.y, slot = rec.z, pos0 = rec.w;
     const int hd = blockIdx.y, vb = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -94,10 +94,10 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
     // all threads: start the copies of the round that begins at token t0 into buffer `buf` (q, k, v as projected; q is scaled when
     // the sums are written)
     auto stage = [&](int t0, int buf) {
-        const int nb = min(MM_TB, n_tok - t0);
+        const int nb = min(TB, n_tok - t0);
         float* qs = sm + buf * ROUND;
-        float* ks = qs + MM_TB * DPP;
-        float* vs = ks + MM_TB * DPP;
+        float* ks = qs + TB * DPP;
+        float* vs = ks + TB * DPP;
         if (vec) {
             for (int i = tid; i < nb * (DP / 4); i += NT) {
                 const int tt = i / (DP / 4), c = (i - tt * (DP / 4)) * 4;
@@ -121,10 +121,10 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
     // gate warp: the log gates of the round (one token per lane), the walk of the stabiliser through them (every lane walks, the
     // gates come by shuffle: one add and one max per token on the critical path), and the three factors of every token
     auto gates = [&](int t0, int buf) {
-        const int nb = min(MM_TB, n_tok - t0);
-        float* ga = sm + buf * ROUND + MM_TB * (2 * DPP + COLS);
-        float* gb = ga + MM_TB;
-        float* gm = gb + MM_TB;
+        const int nb = min(TB, n_tok - t0);
+        float* ga = sm + buf * ROUND + TB * (2 * DPP + COLS);
+        float* gb = ga + TB;
+        float* gm = gb + TB;
         float at = 0.f, bt = 0.f;
         if (lane < nb) {
             const float* pr = a.proj + (size_t)(row0 + t0 + lane) * a.ld_proj + hd;
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
         }
         float m_before = 0.f, m_after = 0.f;
 #pragma unroll
-        for (int tt = 0; tt < MM_TB; tt++) {
+        for (int tt = 0; tt < TB; tt++) {
             const float as = __shfl_sync(0xffffffffu, at, tt), bs = __shfl_sync(0xffffffffu, bt, tt);
             if (tt < nb) {
                 const float mn = fmaxf(bs + m, as);
@@ -151,18 +151,18 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
     stage(0, 0);
     cp_async_commit();
     if (gate_warp) gates(0, 0);
-    for (int t0 = 0, r = 0; t0 < n_tok; t0 += MM_TB, r++) {
-        const int nb = min(MM_TB, n_tok - t0), buf = r & 1;
+    for (int t0 = 0, r = 0; t0 < n_tok; t0 += TB, r++) {
+        const int nb = min(TB, n_tok - t0), buf = r & 1;
         cp_async_wait<0>();                                  // this thread's copies of round r have landed ...
         __syncthreads();                                     // ... and everyone's, with the round's factors; round r - 1 is consumed
-        if (t0 + MM_TB < n_tok) stage(t0 + MM_TB, buf ^ 1);
+        if (t0 + TB < n_tok) stage(t0 + TB, buf ^ 1);
         cp_async_commit();
         const float* qs = sm + buf * ROUND;
-        const float* ks = qs + MM_TB * DPP;
-        const float* vs = ks + MM_TB * DPP;
-        const float* ga = vs + MM_TB * COLS;
-        const float* gb = ga + MM_TB;
-        const float* gm = gb + MM_TB;
+        const float* ks = qs + TB * DPP;
+        const float* vs = ks + TB * DPP;
+        const float* ga = vs + TB * COLS;
+        const float* gb = ga + TB;
+        const float* gm = gb + TB;
         if (main) {
 #pragma unroll 2
             for (int tt = 0; tt < nb; tt++) {
@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
                 }
             }
         } else if (gate_warp) {
-            if (t0 + MM_TB < n_tok) gates(t0 + MM_TB, buf ^ 1);      // the next round's factors, while the main warps work on this one
+            if (t0 + TB < n_tok) gates(t0 + TB, buf ^ 1);      // the next round's factors, while the main warps work on this one
         } else {
             if (first_block) {
 #pragma unroll 4
@@ -278,7 +278,7 @@ extern "C" int64_t p3_matrix_memory_state_floats(int n_heads, int dim, int vdim)
 
 extern "C" int p3_matrix_memory_scan(const p3_matrix_memory_args* a, cudaStream_t st) {
     P3_CHECK_ARG(a && a->proj && a->i_bias && a->f_bias && a->state && a->seqs && a->out && a->den, "matrix_memory_scan: null argument");
-    P3_CHECK_ARG(a->n_heads >= 1 && a->dim >= 1 && a->dim <= 256 && a->vdim >= 1, "matrix_memory_scan: need heads >= 1, 1 <= dim <= 256, vdim >= 1");
+    P3_CHECK_ARG(a->n_heads >= 1 && a->dim >= 1 && a->dim <= 512 && a->vdim >= 1, "matrix_memory_scan: need heads >= 1, 1 <= dim <= 512, vdim >= 1");
     P3_CHECK_ARG(a->gate_cap > 0.f, "matrix_memory_scan: the gate cap must be positive");
     P3_CHECK_ARG(((uintptr_t)a->seqs & 15) == 0, "matrix_memory_scan: the sequence records must be 16-byte aligned");
     if (a->n_seqs == 0) return 0;
@@ -288,14 +288,18 @@ extern "C" int p3_matrix_memory_scan(const p3_matrix_memory_args* a, cudaStream_
     int rs = 4, nc = (int64_t)a->n_seqs * a->n_heads * ((a->vdim + 63) / 64) >= 148 ? 2 : 1;
     if (a->rs_force == 2 || a->rs_force == 4) { rs = a->rs_force; nc = 1; }
     if (a->rs_force == 8) { rs = 4; nc = 2; }
+    if (a->dim > 256) { rs = 4; nc = 1; }                    // 128 rows per thread, 16 tokens per round
     const int per = (a->dim + rs - 1) / rs, ds = per <= 16 ? 16 : per <= 32 ? 32 : per <= 64 ? 64 : 128;
-    const int cols = MM_MAIN * 32 / rs * nc;
+    const int cols = MM_MAIN * 32 / rs * nc, tb = a->dim > 256 ? 16 : MM_TB;
     const dim3 grid((unsigned)a->n_seqs, (unsigned)a->n_heads, (unsigned)((a->vdim + cols - 1) / cols));
-    const size_t bytes = sizeof(float) * (size_t)2 * MM_TB * (2 * (ds * rs + 4 * rs) + cols + 3);   // two staged rounds
+    const size_t bytes = sizeof(float) * (size_t)2 * tb * (2 * (ds * rs + 4 * rs) + cols + 3);   // two staged rounds
 #define GO(DS, RS, NC)                                                                                              \
-    do { if (set_smem_attr(matrix_memory_scan_kernel<DS, RS, NC>, bytes)) return -1;                                  \
-         p3_launch_pdl(matrix_memory_scan_kernel<DS, RS, NC>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a); } while (0)
-    if (rs == 2) { if (ds == 16) GO(16, 2, 1); else if (ds == 32) GO(32, 2, 1); else if (ds == 64) GO(64, 2, 1); else GO(128, 2, 1); }
+    do { if (set_smem_attr(matrix_memory_scan_kernel<DS, RS, NC, MM_TB>, bytes)) return -1;                           \
+         p3_launch_pdl(matrix_memory_scan_kernel<DS, RS, NC, MM_TB>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a); } while (0)
+    if (a->dim > 256) {
+        if (set_smem_attr(matrix_memory_scan_kernel<128, 4, 1, 16>, bytes)) return -1;
+        p3_launch_pdl(matrix_memory_scan_kernel<128, 4, 1, 16>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a);
+    } else if (rs == 2) { if (ds == 16) GO(16, 2, 1); else if (ds == 32) GO(32, 2, 1); else if (ds == 64) GO(64, 2, 1); else GO(128, 2, 1); }
     else if (nc == 1) { if (ds == 16) GO(16, 4, 1); else if (ds == 32) GO(32, 4, 1); else GO(64, 4, 1); }
     else { if (ds == 16) GO(16, 4, 2); else if (ds == 32) GO(32, 4, 2); else GO(64, 4, 2); }
 #undef GO

@@ -580,7 +580,7 @@ def test_token_shift_carries_the_last_row_of_a_slot(lib, W):
     assert torch.isnan(sd[0]).all()                           # a slot without tokens is not touched
 
 
-@pytest.mark.parametrize('shape', [(2, 24, 40), (1, 7, 5), (3, 64, 64), (2, 128, 96), (1, 200, 33), (5, 136, 70)])
+@pytest.mark.parametrize('shape', [(2, 24, 40), (1, 7, 5), (3, 64, 64), (2, 128, 96), (1, 200, 33), (5, 136, 70), (1, 300, 40)])
 @pytest.mark.parametrize('cap,rs', [(15.0, 0), (1.5, 0), (15.0, 2), (15.0, 4), (15.0, 8)])
 def test_matrix_memory_scan_in_portions_and_with_saturated_gates(lib, shape, cap, rs):
     """the recurrence alone: whole sequences against the token loop of the oracle, then the same sequences in portions (the state
