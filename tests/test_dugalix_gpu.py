@@ -508,7 +508,8 @@ def _tile_rows(lib, dtype, H, G, d, dv, window, keep, sigmoid):
     return int(lib.lib().p3_attn_window_tile_rows(C.byref(a)))
 
 
-@pytest.mark.parametrize('shape', [(3, 1, 28, 20), (4, 2, 80, 40), (4, 2, 64, 64), (8, 2, 128, 128), (6, 3, 24, 40), (20, 1, 32, 16)])
+@pytest.mark.parametrize('shape', [(3, 1, 28, 20), (4, 2, 80, 40), (4, 2, 64, 64), (8, 2, 128, 128), (6, 3, 24, 40), (20, 1, 32, 16),
+                                   (2, 1, 264, 40), (4, 2, 160, 136)])
 @pytest.mark.parametrize('sigmoid', [False, True])
 @pytest.mark.parametrize('dtype', [F32, B16])
 @pytest.mark.parametrize('n_splits', [1, 3])
