@@ -362,6 +362,9 @@ typedef struct {
     void* k_pool; void* v_pool; const int32_t* block_table; int32_t bt_stride;
     const int32_t* tok_slot; const int32_t* tok_pos; int32_t T;
     int32_t act_f32, cache_f32;
+    const float* bias;             /* fp32 indexed like proj's columns, or NULL: added to q, k and v before anything else */
+    float q_temp_coef; int32_t q_temp_every;   /* every > 0: the normed query at position p is multiplied by
+                                      1 + coef * ln(floor((p + 1) / every) + 1) */
 } p3_qkv_post_args;
 int p3_qkv_post(const p3_qkv_post_args* args, cudaStream_t st);
 
@@ -387,6 +390,8 @@ typedef struct {
     const float* sig_bias;         /* fp32 [n_heads] or NULL. Not NULL: no softmax; the weight of a visible key is
                                       sigmoid(score + sig_bias[h]) and the weights are not normalised over the keys (sink unused) */
     float out_scale;               /* factor on the head outputs (0 is read as 1) */
+    const float* elem_gate; int64_t ld_elem_gate;   /* fp32 logits [T, ld_elem_gate] or NULL: output column c of a row (head h at
+                                      column h * vdim) is multiplied by sigmoid(elem_gate[row][c]) */
 } p3_attn_window_args;
 /* query rows per tile that p3_attn_window_prefill takes for these sizes: 64 on its tensor-core path, else 32 */
 int p3_attn_window_tile_rows(const p3_attn_window_args* args);
@@ -438,6 +443,14 @@ typedef struct {
     void* cache; const int32_t* block_table; int32_t bt_stride;
     const int32_t* tok_slot; const int32_t* tok_pos; int32_t T;
     int32_t act_f32, cache_f32;
+    /* Queries that come from a second product (through a normed low-rank vector) make this two calls. First, on the input
+     * projection: n_heads = 0, the latent part as above, and the query's low-rank vector (q_rank numbers at cq_off) RMS-normed with
+     * cq_gain -> cq_out (act) [T, ld_cq]. Then, on the product of cq_out with the query up-projection: q_src (fp32 [T, ld_qsrc],
+     * heads x (dim | rot_dim)) replaces proj + q_off and cache = NULL skips the latent part (proj may then be NULL). A layer that
+     * reads another layer's cache makes the first call with cache = NULL too. */
+    int32_t pair_mode;             /* rotation pairs: 0 = number i with i + rot_n / 2, 1 = neighbours 2i and 2i + 1 (freq[i] each) */
+    const float* q_src; int64_t ld_qsrc;
+    int32_t cq_off, q_rank; const float* cq_gain; void* cq_out; int64_t ld_cq;
 } p3_latent_post_args;
 int p3_latent_post(const p3_latent_post_args* args, cudaStream_t st);
 
@@ -533,6 +546,43 @@ int p3_matrix_memory_scan(const p3_matrix_memory_args* args, cudaStream_t st);
  * [T, ld_gate] or NULL */
 int p3_headnorm_gate(const float* y, int64_t ldy, const float* den, int n_heads, int vdim, const float* gain, const float* gate,
                      int64_t ld_gate, float scale, float eps, void* out, int64_t ldo, int out_f32, int64_t T, cudaStream_t st);
+
+
+/* ---- parts of decoders with a hashed token-pair embedding, a gated linear-attention recurrence with a decay per key channel, and
+ * attention whose distance bias is linear (Danalorn and designs built from these parts) */
+
+/* x fp32 [T, W] = table[ids[t]] * scale + pair_table[r] (both bf16; pair_table NULL: no second term), r = (prev * mul_prev +
+ * ids[t] * mul_cur) mod buckets with prev = the token before t in its sequence: the row above inside a step's run of rows, else the
+ * slot's saved token prev_state[slot * state_stride]; r = buckets (the table's last row) for a sequence's first token (position
+ * 0). Afterwards prev_state holds the last token of every sequence of the step. seqs / slot_seq / tok_slot as for p3_token_shift. */
+int p3_embed_pair_rows_f32(const void* table, const void* pair_table, const int32_t* ids, const int32_t* seqs, const int32_t* slot_seq,
+                           const int32_t* tok_slot, int32_t* prev_state, int64_t state_stride, float* x, int64_t T, int W, int vocab,
+                           float scale, int64_t buckets, int64_t mul_prev, int64_t mul_cur, cudaStream_t st);
+
+/* pen[h][i] = slope[h] * i, i < n: the table of a linear distance bias for p3_attn_window_* */
+int p3_distance_linear_table(const float* slope, float* pen, int H, int n, cudaStream_t st);
+
+/* Gated linear attention (csrc/recurrent.cu). Per head a state S [dim][vdim] (dim <= 512), zero at the start of a sequence:
+ *   S' = diag(a) S + k v^T,  y = S'^T q * q_scale,  a[j] = exp(logsigmoid(z[j] + z_bias[j]) * inv_tau)   (sigmoid(z)^(1/tau))
+ * token by token over the rows of every sequence of `seqs`. q at q_off, k at k_off (heads x dim) and v at v_off (heads x vdim) are
+ * columns of proj (fp32 [T, ld_proj]); the decay logits z fp32 [T, ld_z] (heads x dim, z_bias fp32 [heads * dim] or NULL) come from
+ * a product of their own. out fp32 [T, ld_out], head h at column h * vdim. The state of a slot is `state + slot *
+ * p3_gla_state_floats(...)` floats, read at the start and written at the end of the step. rs_force as for the matrix memory. */
+typedef struct {
+    const float* proj; int64_t ld_proj; int32_t q_off, k_off, v_off;
+    const float* z; int64_t ld_z; const float* z_bias; float inv_tau;
+    int32_t n_heads, dim, vdim; float q_scale;
+    float* state; const int32_t* seqs; int32_t n_seqs;
+    float* out; int64_t ld_out; int32_t rs_force;
+} p3_gla_args;
+int64_t p3_gla_state_floats(int n_heads, int dim, int vdim);
+int p3_gla_scan(const p3_gla_args* args, cudaStream_t st);
+
+/* p3_headnorm_gate with two more choices: gain_shared != 0: gain is fp32 [vdim], the same for every head (else [n_heads * vdim]);
+ * gate_silu != 0: the gate is g * sigmoid(g) instead of sigmoid(g) */
+int p3_headnorm_gate_x(const float* y, int64_t ldy, const float* den, int n_heads, int vdim, const float* gain, int gain_shared,
+                       const float* gate, int64_t ld_gate, int gate_silu, float scale, float eps, void* out, int64_t ldo, int out_f32,
+                       int64_t T, cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -85,10 +85,14 @@ _SIGS = {
     'p3_router_groups': [_p, _l, _p, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p],
     'p3_moe_combine_identity': [_p, _l, _p, _p, _p, _i, _i, _p, _p, _l, _p, _l, _i, _p],
     'p3_headnorm_gate': [_p, _l, _p, _i, _i, _p, _p, _l, _f, _f, _p, _l, _i, _l, _p],
+    # hashed token-pair embedding, linear distance bias, head norm with a shared gain / silu gate (csrc/seq_ops.cu, csrc/recurrent.cu)
+    'p3_embed_pair_rows_f32': [_p, _p, _p, _p, _p, _p, _p, _l, _p, _l, _i, _i, _f, _l, _l, _l, _p],
+    'p3_distance_linear_table': [_p, _p, _i, _i, _p],
+    'p3_headnorm_gate_x': [_p, _l, _p, _i, _i, _p, _i, _p, _l, _i, _f, _f, _p, _l, _i, _l, _p],
 }
 ROUTER_SOFTMAX, ROUTER_GROUP_MAX, ROUTER_PLAIN_WEIGHTS = 1, 2, 4          # mode bits of p3_router_groups
 _STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode', 'p3_latent_post',
-                   'p3_qkv_rope_post', 'p3_matrix_memory_scan']
+                   'p3_qkv_rope_post', 'p3_matrix_memory_scan', 'p3_gla_scan']
 ATTN_WINDOW_MMA = os.environ.get('P3_ATTN_WINDOW_MMA', '1') != '0'
 
 _lib = None
@@ -98,7 +102,7 @@ launches = 0          # number of p3_* kernel-launching calls issued (bench.py r
 def exported_symbols():
     return sorted(list(_SIGS) + ['p3_last_error', 'p3_version', 'p3_attention_decode_workspace', 'p3_decode_mega',
                                  'p3_decode_mega_ctas', 'p3_gemm_fused', 'p3_gemm_plan_weights', 'p3_gemm_skinny_x', 'p3_trace_set', 'p3_trace_count',
-                                 'p3_attn_window_tile_rows', 'p3_matrix_memory_state_floats']
+                                 'p3_attn_window_tile_rows', 'p3_matrix_memory_state_floats', 'p3_gla_state_floats']
                   + _STRUCT_ENTRIES)
 
 
@@ -121,6 +125,7 @@ def lib():
                 getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
             L.p3_attn_window_tile_rows.argtypes, L.p3_attn_window_tile_rows.restype = [_p], C.c_int
             L.p3_matrix_memory_state_floats.argtypes, L.p3_matrix_memory_state_floats.restype = [_i, _i, _i], C.c_int64
+            L.p3_gla_state_floats.argtypes, L.p3_gla_state_floats.restype = [_i, _i, _i], C.c_int64
             L.p3_last_error.restype = C.c_char_p
             L.p3_version.restype = C.c_int
             _lib = L
@@ -140,6 +145,7 @@ def lib():
             getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
         L.p3_attn_window_tile_rows.argtypes, L.p3_attn_window_tile_rows.restype = [_p], C.c_int
         L.p3_matrix_memory_state_floats.argtypes, L.p3_matrix_memory_state_floats.restype = [_i, _i, _i], C.c_int64
+        L.p3_gla_state_floats.argtypes, L.p3_gla_state_floats.restype = [_i, _i, _i], C.c_int64
         _lib = L
     return _lib
 
@@ -224,7 +230,8 @@ class QkvPostArgs(C.Structure):
                 ('v_first', _p), ('v_mode', C.c_int32), ('v_lambda', C.c_float),
                 ('q_out', _p), ('ld_q', _l), ('gate_out', _p),
                 ('k_pool', _p), ('v_pool', _p), ('block_table', _p), ('bt_stride', C.c_int32),
-                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32)]
+                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32),
+                ('bias', _p), ('q_temp_coef', C.c_float), ('q_temp_every', C.c_int32)]
 
 
 class AttnWindowArgs(C.Structure):
@@ -234,7 +241,7 @@ class AttnWindowArgs(C.Structure):
                 ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('scale', C.c_float),
                 ('window', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32), ('tiles', _p), ('n_tiles', C.c_int32),
                 ('n_splits', C.c_int32), ('ws', _p), ('v_ld', C.c_int32), ('keep_first', C.c_int32), ('sig_bias', _p),
-                ('out_scale', C.c_float)]
+                ('out_scale', C.c_float), ('elem_gate', _p), ('ld_elem_gate', _l)]
 
 
 class LatentPostArgs(C.Structure):
@@ -245,7 +252,9 @@ class LatentPostArgs(C.Structure):
                 ('c_gain', _p), ('eps', C.c_float), ('freq', _p), ('rot_mag', C.c_float),
                 ('q_plain', _p), ('ld_qp', _l), ('q_lat', _p), ('ld_ql', _l), ('hid', _p), ('ld_hid', _l), ('hid_off', C.c_int32),
                 ('cache', _p), ('block_table', _p), ('bt_stride', C.c_int32),
-                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32)]
+                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32),
+                ('pair_mode', C.c_int32), ('q_src', _p), ('ld_qsrc', _l), ('cq_off', C.c_int32), ('q_rank', C.c_int32),
+                ('cq_gain', _p), ('cq_out', _p), ('ld_cq', _l)]
 
 
 class QkvRopePostArgs(C.Structure):
@@ -263,3 +272,11 @@ class MatrixMemoryArgs(C.Structure):
                 ('i_off', C.c_int32), ('f_off', C.c_int32), ('i_bias', _p), ('f_bias', _p),
                 ('n_heads', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('q_scale', C.c_float), ('gate_cap', C.c_float),
                 ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l), ('den', _p), ('rs_force', C.c_int32)]
+
+
+class GlaArgs(C.Structure):
+    """p3_gla_args (include/phi3_b200.h)"""
+    _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('k_off', C.c_int32), ('v_off', C.c_int32),
+                ('z', _p), ('ld_z', _l), ('z_bias', _p), ('inv_tau', C.c_float),
+                ('n_heads', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('q_scale', C.c_float),
+                ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l), ('rs_force', C.c_int32)]

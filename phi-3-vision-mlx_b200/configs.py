@@ -371,3 +371,129 @@ def tiny_dugalix(width=96, vocab=300, layers=None, eps=1e-5, residual_mult=0.7):
                   dict(sig(3, 3, 24, 90, 8), mlp=moe(32, 4, 0, 2))]
     return {'architecture': 'Dugalix', 'vocab': vocab, 'width': width, 'norm': {'eps': eps}, 'residual_mult': residual_mult,
             'layers': layers}
+
+
+# ------------------------------------------------------------------------------------------------ Danalorn
+class DanalornConfig:
+    """config.json of a Danalorn checkpoint: {"architecture": "Danalorn", "vocab", "width", "norm": {"eps"}, "embedding": {"scale",
+    "bigram": {"buckets", "mul_prev", "mul_cur"} or absent}, "layers": [...]}. A layer entry has "type", "mixer" and "mlp":
+      type "latent_attention": mixer = {heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, mask: {size}, rot: {base, dims}, kv_from}:
+                        per head `dim` plain and `rot_dim` turning query/key numbers, queries through a normed vector of q_rank
+                        numbers, a sliding window and a learned per-head sink; with kv_from = j the layer has no latent projection
+                        and reads the cache of layer j (same kv_rank, rot_dim and rotation);
+      type "attention": mixer = {heads, kv_heads, dim, vdim, scale, q_temp: {coef, every}}: biased projections, per-head query/key
+                        norm, no rotation, a linear distance bias with the fixed slopes 2^(-8 (h + 1) / heads), one added to the
+                        softmax denominator, an element-wise sigmoid output gate; causal without a window;
+      type "gla":       mixer = {heads, dim, vdim, tau}: gated linear attention, decay = sigmoid(z)^(1/tau) per key channel;
+      mlp: null | {"kind": "dense", ff}: a relu^2 unit.
+    Absent optional keys mean: no pair table, no window, no query temperature. Nothing is assumed equal between layers."""
+    SLOPE_OCTAVES = 8.0          # the distance-bias slopes of an attention mixer span 2^-8 .. 1: fixed by the design
+
+    def __init__(self, d):
+        self.raw = d
+        self.architecture = d.get('architecture', 'Danalorn')
+        self.architectures = [self.architecture]
+        self.vocab_size, self.width = int(d['vocab']), int(d['width'])
+        self.eps = float(d['norm']['eps'])
+        emb = d.get('embedding') or {}
+        self.embed_scale = float(emb.get('scale', 1.0))
+        bg = emb.get('bigram')
+        self.bigram = None if not bg else SimpleNamespace(buckets=int(bg['buckets']), mul_prev=int(bg['mul_prev']),
+                                                          mul_cur=int(bg['mul_cur']))
+        if self.bigram is not None and self.bigram.buckets < 1:
+            raise ValueError('embedding.bigram.buckets must be at least 1')
+        self.layers = []
+        for i, lc in enumerate(d['layers']):
+            kind, m = lc.get('type'), lc['mixer']
+            if kind == 'latent_attention':
+                r = m.get('rot') or {}
+                mixer = SimpleNamespace(kind=kind, heads=int(m['heads']), dim=int(m['dim']), rot_dim=int(m.get('rot_dim', 0)),
+                                        vdim=int(m.get('vdim', m['dim'])), kv_rank=int(m['kv_rank']), q_rank=int(m['q_rank']),
+                                        scale=float(m['scale']), window=int((m.get('mask') or {}).get('size') or 0),
+                                        kv_from=None if m.get('kv_from') is None else int(m['kv_from']), rot=None)
+                if mixer.rot_dim > 0:
+                    mixer.rot = SimpleNamespace(base=float(r['base']), dims=int(r.get('dims', mixer.rot_dim)))
+                    if mixer.rot.dims % 2 or not 0 < mixer.rot.dims <= mixer.rot_dim:
+                        raise ValueError(f'layer {i}: rot.dims must be even and at most rot_dim')
+                if mixer.kv_from is not None:
+                    j = mixer.kv_from
+                    src = self.layers[j].mixer if 0 <= j < i else None
+                    if src is None or src.kind != kind or src.kv_from is not None:
+                        raise ValueError(f'layer {i}: kv_from must name an earlier latent_attention layer with a latent projection of its own')
+                    if (src.kv_rank, src.rot_dim) != (mixer.kv_rank, mixer.rot_dim) or \
+                            (src.rot and (src.rot.base, src.rot.dims)) != (mixer.rot and (mixer.rot.base, mixer.rot.dims)):
+                        raise ValueError(f'layer {i}: kv_rank, rot_dim and rotation must equal those of layer {j}')
+            elif kind == 'attention':
+                qt = m.get('q_temp') or {}
+                mixer = SimpleNamespace(kind=kind, heads=int(m['heads']), kv_heads=int(m.get('kv_heads', m['heads'])), dim=int(m['dim']),
+                                        vdim=int(m.get('vdim', m['dim'])), scale=float(m['scale']),
+                                        q_temp_coef=float(qt.get('coef', 0.0)), q_temp_every=int(qt.get('every', 0)))
+                if mixer.heads % mixer.kv_heads:
+                    raise ValueError(f'layer {i}: heads must be a multiple of kv_heads')
+                if mixer.dim > 256 or mixer.vdim > 256:
+                    raise NotImplementedError(f'layer {i}: head sizes above 256; the query/key norm kernel takes up to 256')
+            elif kind == 'gla':
+                mixer = SimpleNamespace(kind=kind, heads=int(m['heads']), dim=int(m['dim']), vdim=int(m.get('vdim', m['dim'])),
+                                        tau=float(m['tau']))
+                if not 1 <= mixer.dim <= 512:
+                    raise NotImplementedError(f'layer {i}: key size {mixer.dim} of the recurrence; the kernels take 1 .. 512')
+                if mixer.tau <= 0:
+                    raise ValueError(f'layer {i}: tau must be positive')
+            else:
+                raise NotImplementedError(f'layer {i}: mixer type {kind!r} is not part of this design')
+            f = lc.get('mlp')
+            if f is None:
+                ff = None
+            elif f['kind'] == 'dense':
+                ff = SimpleNamespace(kind='dense', ff=int(f['ff']))
+            else:
+                raise NotImplementedError(f"layer {i}: feed-forward kind {f['kind']!r}")
+            self.layers.append(SimpleNamespace(mixer=mixer, ff=ff))
+        self.num_hidden_layers = len(self.layers)
+
+    def kv_layout(self):
+        """per layer (kv heads, key size, value size): what the page pool allocates. A latent layer caches one row (latent vector |
+        turning key part) per token as one shared head; a layer that reads another layer's cache, and a recurrent layer, nothing."""
+        out = []
+        for l in self.layers:
+            m = l.mixer
+            if m.kind == 'attention':
+                out.append((m.kv_heads, m.dim, m.vdim))
+            elif m.kind == 'latent_attention' and m.kv_from is None:
+                out.append((1, m.kv_rank + m.rot_dim, 0))
+            else:
+                out.append((0, 0, 0))
+        return out
+
+    def slopes(self, heads):
+        """slope of the linear distance bias of head h = 0 .. heads - 1"""
+        return [2.0 ** (-self.SLOPE_OCTAVES * (h + 1) / heads) for h in range(heads)]
+
+
+def tiny_danalorn(width=96, vocab=300, layers=None, eps=1e-5, bigram=(257, 29, 5), embed_scale=7.0):
+    """A small Danalorn config dict for tests: sizes deliberately unequal between layers (dim != vdim != rot_dim, heads != kv_heads,
+    partly rotated turning parts, windows that differ), a latent layer that reads an earlier layer's cache, one layer without a
+    feed-forward, an attention layer without a query temperature."""
+    la = lambda heads, dim, rd, vdim, rank, qrank, win, rdims=None, base=10000.0, kv_from=None: {
+        'type': 'latent_attention',
+        'mixer': dict(heads=heads, dim=dim, rot_dim=rd, vdim=vdim, kv_rank=rank, q_rank=qrank, scale=(dim + rd) ** -0.5,
+                      rot={'base': base, 'dims': rdims or rd}, **({'mask': {'size': win}} if win else {}),
+                      **({'kv_from': kv_from} if kv_from is not None else {}))}
+    att = lambda heads, kv, dim, vdim, qt=None: {
+        'type': 'attention', 'mixer': dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=dim ** -0.5,
+                                           **({'q_temp': {'coef': qt[0], 'every': qt[1]}} if qt else {}))}
+    gla = lambda heads, dim, vdim, tau: {'type': 'gla', 'mixer': dict(heads=heads, dim=dim, vdim=vdim, tau=tau)}
+    dense = lambda ff: {'kind': 'dense', 'ff': ff}
+    if layers is None:
+        layers = [dict(gla(3, 24, 40, 8.0), mlp=dense(136)),
+                  dict(la(5, 16, 8, 24, 40, 56, 37), mlp=dense(72)),
+                  dict(att(6, 3, 24, 40, (0.4, 7)), mlp=None),
+                  dict(la(3, 24, 8, 16, 40, 32, 70, kv_from=1), mlp=dense(40)),
+                  dict(att(4, 1, 40, 24), mlp=dense(88)),
+                  dict(la(4, 8, 24, 32, 48, 40, 0, rdims=16, base=500.0), mlp=dense(56)),
+                  dict(gla(2, 40, 72, 3.0), mlp=dense(64))]
+    d = {'architecture': 'Danalorn', 'vocab': vocab, 'width': width, 'norm': {'eps': eps}, 'embedding': {'scale': embed_scale},
+         'layers': layers}
+    if bigram:
+        d['embedding']['bigram'] = {'buckets': bigram[0], 'mul_prev': bigram[1], 'mul_cur': bigram[2]}
+    return d

@@ -28,6 +28,11 @@ template <typename T> __device__ __forceinline__ void stv(T* p, float v);
 template <> __device__ __forceinline__ void stv<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stv<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// element-wise output gate: sigmoid of the logit that belongs to output column `col` of batch row `row` (1 without such a gate)
+__device__ __forceinline__ float elem_gate(const p3_attn_window_args& a, size_t row, size_t col) {
+    return a.elem_gate ? 1.0f / (1.0f + expf(-a.elem_gate[row * a.ld_elem_gate + col])) : 1.f;
+}
+
 constexpr int BQ = 32, WARPS = 4, RPW = BQ / WARPS;          // prefill: query rows per CTA / per warp
 constexpr int WIDE = 256;                                    // fp32 kernels: key numbers per chunk, value columns per CTA
 
@@ -184,7 +189,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
 #pragma unroll
         for (int j = 0; j < DVC; j++) {
             const int c = lane + 32 * j;
-            if (c < dv) stv(out + (size_t)(row0 + qr) * a.ld_out + (size_t)h * a.vdim + vc0 + c, acc[r][j] * inv);
+            if (c < dv) {
+                const size_t oc = (size_t)h * a.vdim + vc0 + c;
+                stv(out + (size_t)(row0 + qr) * a.ld_out + oc, acc[r][j] * inv * elem_gate(a, row0 + qr, oc));
+            }
         }
     }
 }
@@ -407,8 +415,11 @@ __global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_a
 #pragma unroll
         for (int n = 0; n < DN; n++) {
             const int c = n * 8 + tig * 2;
-            if (c < dv)
-                *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + row) * a.ld_out + c) = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+            if (c < dv) {
+                const size_t oc = (size_t)h * a.vdim + vc0 + c;
+                *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + row) * a.ld_out + c) =
+                    pack_bf16(o[n][half * 2] * inv * elem_gate(a, row0 + row, oc), o[n][half * 2 + 1] * inv * elem_gate(a, row0 + row, oc + 1));
+            }
         }
     }
 }
@@ -566,7 +577,8 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
             }
             if (n_splits == 1) {
                 const float gate = (a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
-                stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c, L > 0.f ? o * gate / (sig ? 1.f : L) : 0.f);
+                const size_t oc = (size_t)(hb + r) * a.vdim + vc0 + c;
+                stv((AT*)a.out + (size_t)row * a.ld_out + oc, L > 0.f ? o * gate / (sig ? 1.f : L) * elem_gate(a, row, oc) : 0.f);
             } else {
                 float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (a.vdim + 2);
                 if (c == 0 && vc0 == 0) { w[0] = M; w[1] = L; }            // every column block forms the same maximum and sum
@@ -786,7 +798,8 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
             }
             if (n_splits == 1) {
                 const float gate = (a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
-                ((bf16*)a.out)[(size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c] = __float2bfloat16_rn(L > 0.f ? acc * gate / (sig ? 1.f : L) : 0.f);
+                const size_t oc = (size_t)(hb + r) * a.vdim + vc0 + c;
+                ((bf16*)a.out)[(size_t)row * a.ld_out + oc] = __float2bfloat16_rn(L > 0.f ? acc * gate / (sig ? 1.f : L) * elem_gate(a, row, oc) : 0.f);
             } else {
                 float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (a.vdim + 2);
                 if (c == 0 && vc0 == 0) { w[0] = M; w[1] = L; }            // every column block forms the same maximum and sum
@@ -821,7 +834,8 @@ __global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, in
             L = fmaf(ls, f, L);
             o = fmaf(os, f, o);
         }
-        stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)h * dv + c, L > 0.f ? o * gate / (sig ? 1.f : L) : 0.f);
+        const size_t oc = (size_t)h * dv + c;
+        stv((AT*)a.out + (size_t)row * a.ld_out + oc, L > 0.f ? o * gate / (sig ? 1.f : L) * elem_gate(a, row, oc) : 0.f);
     }
 }
 

@@ -24,7 +24,17 @@
 //                               m per 32 value columns: every CTA needs m at its start and the first CTA to finish must not
 //                               overwrite what another still has to read, so a CTA reads the copy of its first 32 columns and
 //                               rewrites those of all its columns.
-//   headnorm_gate_kernel        y / rms(y over the head) * gain * sigmoid(gate logits) * scale -> activation type
+//   headnorm_gate_kernel        y / rms(y over the head) * gain * sigmoid(gate logits) * scale -> activation type (the gate may also
+//                               be silu, the gain one vector shared by the heads)
+//
+// Gated linear attention (Yang et al., "Gated Linear Attention Transformers with Hardware-Efficient Training"). Per head a state
+// S [dim][vdim] that starts at zero, with one decay per key channel and token:
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T        y_t = S_t^T q_t        a_t = sigmoid(z_t)^(1/tau) = exp(logsigmoid(z_t) / tau)
+//   gla_scan_kernel             the matrix-memory scan's layout (columns of S in registers, rounds of staged tokens, async copies one
+//                               round ahead) with a staged row of decays beside every k and q row; the two helper warps turn the
+//                               decay logits of the next round into decays while the main warps work on this one. There is no
+//                               normaliser and no stabiliser: every factor is in (0, 1]. As there, a token's arithmetic does not
+//                               depend on how the sequence was cut into steps.
 #include "common.cuh"
 #include "../../include/phi3_b200.h"
 #include <cfloat>
@@ -231,12 +241,147 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
     }
 }
 
+__host__ __device__ inline int64_t gla_head_floats(int dim, int vdim) { return (int64_t)dim * vdim; }
+
+template <int DS, int RS, int NC, int TB>
+__global__ void __launch_bounds__(MM_WARPS * 32) gla_scan_kernel(p3_gla_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    // a warp = RS row slices x CW lanes, every lane with NC columns (CW apart); DP: dim rounded up
+    constexpr int CW = 32 / RS, WCOLS = CW * NC, COLS = MM_MAIN * WCOLS, DP = DS * RS;
+    constexpr int NT = MM_WARPS * 32, NH = NT - MM_MAIN * 32;   // all threads; threads of the helper warps
+    constexpr int DPP = DP + 4 * RS;                         // pitch of a staged row: its RS slices 4 floats apart (bank spread)
+    constexpr int ROUND = TB * (3 * DPP + COLS);             // floats of one staged round
+    auto at_row = [](int c) { return c + 4 * (c / DS); };    // where number c of a row lives
+    extern __shared__ __align__(16) float sm[];
+    const int d = a.dim, dv = a.vdim, H = a.n_heads;
+    // two rounds in flight: [q [TB][DPP] (zeros beyond dim) | k alike | decays alike | v [TB][COLS]]
+    const int4 rec = reinterpret_cast<const int4*>(a.seqs)[blockIdx.x];
+    const int row0 = rec.x, n_tok = rec.y, slot = rec.z, pos0 = rec.w;
+    const int hd = blockIdx.y, vb = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool fresh = pos0 == 0, main = warp < MM_MAIN;
+    float* Sg = a.state + ((size_t)slot * H + hd) * gla_head_floats(d, dv);
+    const int col = vb * COLS + warp * WCOLS + lane % CW, d0 = (lane / CW) * DS;   // first of this lane's columns
+    float S[NC][DS];
+    if (main) {
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int j = 0; j < DS; j++)
+                S[c][j] = (!fresh && col + c * CW < dv && d0 + j < d) ? Sg[(size_t)(d0 + j) * dv + col + c * CW] : 0.f;
+    }
+    const bool vec = d % 4 == 0 && a.ld_proj % 4 == 0 && a.q_off % 4 == 0 && a.k_off % 4 == 0 && ((uintptr_t)a.proj & 15) == 0;
+
+    // all threads: start the copies of the round that begins at token t0 into buffer `buf`
+    auto stage = [&](int t0, int buf) {
+        const int nb = min(TB, n_tok - t0);
+        float* qs = sm + buf * ROUND;
+        float* ks = qs + TB * DPP;
+        float* vs = ks + 2 * TB * DPP;
+        if (vec) {
+            for (int i = tid; i < nb * (DP / 4); i += NT) {
+                const int tt = i / (DP / 4), c = (i - tt * (DP / 4)) * 4;
+                const float* pr = a.proj + (size_t)(row0 + t0 + tt) * a.ld_proj + (size_t)hd * d + (c < d ? c : 0);
+                cp_async16(smem_u32(qs + tt * DPP + at_row(c)), pr + a.q_off, c < d ? 16 : 0);
+                cp_async16(smem_u32(ks + tt * DPP + at_row(c)), pr + a.k_off, c < d ? 16 : 0);
+            }
+        } else {
+            for (int i = tid; i < nb * DP; i += NT) {
+                const int tt = i / DP, c = i - tt * DP;
+                const float* pr = a.proj + (size_t)(row0 + t0 + tt) * a.ld_proj + (size_t)hd * d + (c < d ? c : 0);
+                cp_async4z(smem_u32(qs + tt * DPP + at_row(c)), pr + a.q_off, c < d ? 4 : 0);
+                cp_async4z(smem_u32(ks + tt * DPP + at_row(c)), pr + a.k_off, c < d ? 4 : 0);
+            }
+        }
+        for (int i = tid; i < nb * COLS; i += NT) {
+            const int tt = i / COLS, c = vb * COLS + (i - tt * COLS);
+            cp_async4z(smem_u32(vs + i), a.proj + (size_t)(row0 + t0 + tt) * a.ld_proj + a.v_off + (size_t)hd * dv + (c < dv ? c : 0), c < dv ? 4 : 0);
+        }
+    };
+    // helper warps: the decays of the round, exp(logsigmoid(z + bias) / tau), four independent numbers per thread and pass
+    auto decays = [&](int t0, int buf) {
+        const int nb = min(TB, n_tok - t0), me = tid - MM_MAIN * 32;
+        float* as = sm + buf * ROUND + 2 * TB * DPP;
+        for (int i0 = me; i0 < nb * DP; i0 += 4 * NH) {
+            float z[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * NH, tt = i / DP, c = i - tt * DP;
+                z[u] = (i < nb * DP && c < d) ? a.z[(size_t)(row0 + t0 + tt) * a.ld_z + (size_t)hd * d + c] + (a.z_bias ? a.z_bias[hd * d + c] : 0.f)
+                                              : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * NH, tt = i / DP, c = i - tt * DP;
+                if (i < nb * DP) as[tt * DPP + at_row(c)] = c < d ? expf(log_sigmoid(z[u]) * a.inv_tau) : 0.f;
+            }
+        }
+    };
+
+    stage(0, 0);
+    cp_async_commit();
+    if (!main) decays(0, 0);
+    for (int t0 = 0, r = 0; t0 < n_tok; t0 += TB, r++) {
+        const int nb = min(TB, n_tok - t0), buf = r & 1;
+        cp_async_wait<0>();                                  // this thread's copies of round r have landed ...
+        __syncthreads();                                     // ... and everyone's, with the round's decays; round r - 1 is consumed
+        if (t0 + TB < n_tok) stage(t0 + TB, buf ^ 1);
+        cp_async_commit();
+        const float* qs = sm + buf * ROUND;
+        const float* ks = qs + TB * DPP;
+        const float* as = ks + TB * DPP;
+        const float* vs = as + TB * DPP;
+        if (main) {
+#pragma unroll 2
+            for (int tt = 0; tt < nb; tt++) {
+                float tv[NC], acc[NC][4];
+#pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    tv[c] = vs[tt * COLS + warp * WCOLS + lane % CW + c * CW];
+                    acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+                }
+                const float4* kq = reinterpret_cast<const float4*>(ks + tt * DPP + at_row(d0));
+                const float4* qq = reinterpret_cast<const float4*>(qs + tt * DPP + at_row(d0));
+                const float4* aq = reinterpret_cast<const float4*>(as + tt * DPP + at_row(d0));
+#pragma unroll
+                for (int j = 0; j < DS; j += 4) {
+                    const float4 kk = kq[j / 4], qv = qq[j / 4], al = aq[j / 4];
+#pragma unroll
+                    for (int c = 0; c < NC; c++) {
+                        S[c][j] = fmaf(kk.x, tv[c], al.x * S[c][j]);         acc[c][0] = fmaf(S[c][j], qv.x, acc[c][0]);
+                        S[c][j + 1] = fmaf(kk.y, tv[c], al.y * S[c][j + 1]); acc[c][1] = fmaf(S[c][j + 1], qv.y, acc[c][1]);
+                        S[c][j + 2] = fmaf(kk.z, tv[c], al.z * S[c][j + 2]); acc[c][2] = fmaf(S[c][j + 2], qv.z, acc[c][2]);
+                        S[c][j + 3] = fmaf(kk.w, tv[c], al.w * S[c][j + 3]); acc[c][3] = fmaf(S[c][j + 3], qv.w, acc[c][3]);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    float y = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
+                    if (RS >= 2) y += __shfl_xor_sync(0xffffffffu, y, CW);
+                    if (RS >= 4) y += __shfl_xor_sync(0xffffffffu, y, 2 * CW);
+                    if (lane < CW && col + c * CW < dv)
+                        a.out[(size_t)(row0 + t0 + tt) * a.ld_out + (size_t)hd * dv + col + c * CW] = y * a.q_scale;
+                }
+            }
+        } else {
+            if (t0 + TB < n_tok) decays(t0 + TB, buf ^ 1);    // the next round's decays, while the main warps work on this one
+        }
+    }
+    if (main) {
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int j = 0; j < DS; j++)
+                if (col + c * CW < dv && d0 + j < d) Sg[(size_t)(d0 + j) * dv + col + c * CW] = S[c][j];
+    }
+}
+
 // one warp per (token, head)
 template <typename AT>
 __global__ void headnorm_gate_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ den, int H, int dv,
-                                     const float* __restrict__ gain,
-                                     const float* __restrict__ gate, int64_t ld_gate, float scale, float eps, AT* __restrict__ out,
-                                     int64_t ldo, int64_t T) {
+                                     const float* __restrict__ gain, int gain_shared,
+                                     const float* __restrict__ gate, int64_t ld_gate, int gate_silu, float scale, float eps,
+                                     AT* __restrict__ out, int64_t ldo, int64_t T) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int lane = threadIdx.x & 31;
@@ -254,14 +399,19 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ y, int64_t ldy, c
     for (int i = lane + 256; i < dv; i += 32) { const float u = yr[i] / dn; ss = fmaf(u, u, ss); }
     ss = warp_sum(ss);
     const float r = scale / sqrtf(ss / (float)dv + eps);
+    auto gated = [&](int c) {                                // the gate of output column c: sigmoid(g), or silu(g) = g sigmoid(g)
+        if (!gate) return 1.f;
+        const float g = gate[t * ld_gate + c], sg = 1.0f / (1.0f + expf(-g));
+        return gate_silu ? g * sg : sg;
+    };
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int i = lane + 32 * k, c = h * dv + i;
-        if (i < dv) stv(out + t * ldo + c, v[k] * r * gain[c] * (gate ? 1.0f / (1.0f + expf(-gate[t * ld_gate + c])) : 1.f));
+        if (i < dv) stv(out + t * ldo + c, v[k] * r * gain[gain_shared ? i : c] * gated(c));
     }
     for (int i = lane + 256; i < dv; i += 32) {
         const int c = h * dv + i;
-        stv(out + t * ldo + c, yr[i] / dn * r * gain[c] * (gate ? 1.0f / (1.0f + expf(-gate[t * ld_gate + c])) : 1.f));
+        stv(out + t * ldo + c, yr[i] / dn * r * gain[gain_shared ? i : c] * gated(c));
     }
 }
 template <typename K>
@@ -307,14 +457,51 @@ extern "C" int p3_matrix_memory_scan(const p3_matrix_memory_args* a, cudaStream_
     return 0;
 }
 
-extern "C" int p3_headnorm_gate(const float* y, int64_t ldy, const float* den, int n_heads, int vdim, const float* gain, const float* gate,
-                                int64_t ld_gate, float scale, float eps, void* out, int64_t ldo, int out_f32, int64_t T, cudaStream_t st) {
+extern "C" int p3_headnorm_gate_x(const float* y, int64_t ldy, const float* den, int n_heads, int vdim, const float* gain, int gain_shared,
+                                  const float* gate, int64_t ld_gate, int gate_silu, float scale, float eps, void* out, int64_t ldo,
+                                  int out_f32, int64_t T, cudaStream_t st) {
     P3_CHECK_ARG(y && gain && out && n_heads >= 1 && vdim >= 1, "headnorm_gate: null argument");
     if (T == 0) return 0;
     const int64_t jobs = T * n_heads;
     const unsigned grid = (unsigned)((jobs + 3) / 4);
-    if (out_f32) p3_launch_pdl(headnorm_gate_kernel<float>, dim3(grid), dim3(128), (size_t)(0), st, y, ldy, den, n_heads, vdim, gain, gate, ld_gate, scale, eps, (float*)out, ldo, T);
-    else p3_launch_pdl(headnorm_gate_kernel<bf16>, dim3(grid), dim3(128), (size_t)(0), st, y, ldy, den, n_heads, vdim, gain, gate, ld_gate, scale, eps, (bf16*)out, ldo, T);
+    if (out_f32) p3_launch_pdl(headnorm_gate_kernel<float>, dim3(grid), dim3(128), (size_t)(0), st, y, ldy, den, n_heads, vdim, gain, gain_shared, gate, ld_gate, gate_silu, scale, eps, (float*)out, ldo, T);
+    else p3_launch_pdl(headnorm_gate_kernel<bf16>, dim3(grid), dim3(128), (size_t)(0), st, y, ldy, den, n_heads, vdim, gain, gain_shared, gate, ld_gate, gate_silu, scale, eps, (bf16*)out, ldo, T);
     P3_CHECK_LAUNCH("headnorm_gate");
+    return 0;
+}
+
+extern "C" int p3_headnorm_gate(const float* y, int64_t ldy, const float* den, int n_heads, int vdim, const float* gain, const float* gate,
+                                int64_t ld_gate, float scale, float eps, void* out, int64_t ldo, int out_f32, int64_t T, cudaStream_t st) {
+    return p3_headnorm_gate_x(y, ldy, den, n_heads, vdim, gain, 0, gate, ld_gate, 0, scale, eps, out, ldo, out_f32, T, st);
+}
+
+extern "C" int64_t p3_gla_state_floats(int n_heads, int dim, int vdim) { return (int64_t)n_heads * gla_head_floats(dim, vdim); }
+
+extern "C" int p3_gla_scan(const p3_gla_args* a, cudaStream_t st) {
+    P3_CHECK_ARG(a && a->proj && a->z && a->state && a->seqs && a->out, "gla_scan: null argument");
+    P3_CHECK_ARG(a->n_heads >= 1 && a->dim >= 1 && a->dim <= 512 && a->vdim >= 1, "gla_scan: need heads >= 1, 1 <= dim <= 512, vdim >= 1");
+    P3_CHECK_ARG(((uintptr_t)a->seqs & 15) == 0, "gla_scan: the sequence records must be 16-byte aligned");
+    if (a->n_seqs == 0) return 0;
+    // the shape of a warp as for the matrix memory: four row slices x eight lanes, two columns per lane when that still leaves a
+    // CTA for every SM
+    int rs = 4, nc = (int64_t)a->n_seqs * a->n_heads * ((a->vdim + 63) / 64) >= 148 ? 2 : 1;
+    if (a->rs_force == 2 || a->rs_force == 4) { rs = a->rs_force; nc = 1; }
+    if (a->rs_force == 8) { rs = 4; nc = 2; }
+    if (a->dim > 256) { rs = 4; nc = 1; }                    // 128 rows per thread, 16 tokens per round
+    const int per = (a->dim + rs - 1) / rs, ds = per <= 16 ? 16 : per <= 32 ? 32 : per <= 64 ? 64 : 128;
+    const int cols = MM_MAIN * 32 / rs * nc, tb = a->dim > 256 ? 16 : MM_TB;
+    const dim3 grid((unsigned)a->n_seqs, (unsigned)a->n_heads, (unsigned)((a->vdim + cols - 1) / cols));
+    const size_t bytes = sizeof(float) * (size_t)2 * tb * (3 * (ds * rs + 4 * rs) + cols);   // two staged rounds
+#define GO(DS, RS, NC)                                                                                              \
+    do { if (set_smem_attr(gla_scan_kernel<DS, RS, NC, MM_TB>, bytes)) return -1;                                     \
+         p3_launch_pdl(gla_scan_kernel<DS, RS, NC, MM_TB>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a); } while (0)
+    if (a->dim > 256) {
+        if (set_smem_attr(gla_scan_kernel<128, 4, 1, 16>, bytes)) return -1;
+        p3_launch_pdl(gla_scan_kernel<128, 4, 1, 16>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a);
+    } else if (rs == 2) { if (ds == 16) GO(16, 2, 1); else if (ds == 32) GO(32, 2, 1); else if (ds == 64) GO(64, 2, 1); else GO(128, 2, 1); }
+    else if (nc == 1) { if (ds == 16) GO(16, 4, 1); else if (ds == 32) GO(32, 4, 1); else GO(64, 4, 1); }
+    else { if (ds == 16) GO(16, 4, 2); else if (ds == 32) GO(32, 4, 2); else GO(64, 4, 2); }
+#undef GO
+    P3_CHECK_LAUNCH("gla_scan");
     return 0;
 }

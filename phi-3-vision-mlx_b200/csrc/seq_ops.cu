@@ -129,16 +129,23 @@ __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
         if (job < H + G) {                                   // query or key head: RMS norm over its d numbers, shared gain
             const bool isq = job < H;
             const int h = isq ? job : job - H;
-            const float* src = pr + (isq ? a.q_off : a.k_off) + (size_t)h * d;
+            const int c0 = (isq ? a.q_off : a.k_off) + h * d;
+            const float* src = pr + c0;
             const float* gain = isq ? a.q_gain : a.k_gain;
             float sv[8], gv[8];
             float ss = 0.f;
 #pragma unroll
-            for (int k = 0; k < 8; k++) { const int i = lane + 32 * k; sv[k] = i < d ? src[i] : 0.f; gv[k] = i < d ? gain[i] : 0.f; }
+            for (int k = 0; k < 8; k++) {
+                const int i = lane + 32 * k;
+                sv[k] = i < d ? src[i] + (a.bias ? a.bias[c0 + i] : 0.f) : 0.f;
+                gv[k] = i < d ? gain[i] : 0.f;
+            }
 #pragma unroll
             for (int k = 0; k < 8; k++) ss = fmaf(sv[k], sv[k], ss);
             ss = warp_sum(ss);
-            const float r = 1.0f / sqrtf(ss / (float)d + a.eps);
+            float r = 1.0f / sqrtf(ss / (float)d + a.eps);
+            // query temperature: a factor that grows with the logarithm of the position counted in steps of q_temp_every
+            if (isq && a.q_temp_every > 0) r *= 1.0f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every) + 1.0f);
             if (isq) {
                 AT* dst = (AT*)a.q_out + (size_t)t * a.ld_q + (size_t)h * d;
 #pragma unroll
@@ -150,14 +157,15 @@ __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
             }
         } else {                                             // value head: v, or (1 - lam) v + lam v_first; the mixed v is cached
             const int h = job - H - G;
-            const float* src = pr + a.v_off + (size_t)h * dv;
+            const int c0 = a.v_off + h * dv;
+            const float* src = pr + c0;
             float* vf = a.v_first ? a.v_first + (size_t)t * G * dv + (size_t)h * dv : nullptr;
             CT* dst = (CT*)a.v_pool + (((size_t)page * G + h) * P3_PAGE + off) * dv;
             float sv[8], fv[8];
 #pragma unroll
             for (int k = 0; k < 8; k++) {
                 const int i = lane + 32 * k;
-                sv[k] = i < dv ? src[i] : 0.f;
+                sv[k] = i < dv ? src[i] + (a.bias ? a.bias[c0 + i] : 0.f) : 0.f;
                 fv[k] = (i < dv && a.v_mode == 2) ? vf[i] : 0.f;
             }
 #pragma unroll
@@ -420,8 +428,20 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
     const int page = a.block_table[(size_t)slot * a.bt_stride + pos / P3_PAGE], off = pos % P3_PAGE;
     const int H = a.n_heads, d = a.dim, dr = a.rot_dim, R = a.kv_rank, half = a.rot_n / 2;
     const float fpos = (float)pos;
-    for (int job = blockIdx.y * nw + warp; job < 1 + H; job += gridDim.y * nw) {
-        if (job == 0) {
+    // where the two numbers of rotation pair i live in a turning part
+    const int pa = a.pair_mode ? 2 : 1, pb = a.pair_mode ? 1 : half;
+    for (int job = blockIdx.y * nw + warp; job < 2 + H; job += gridDim.y * nw) {
+        if (job == 1 + H) {                                  // the query's low-rank vector: RMS norm -> input of the query up-projection
+            if (a.q_rank <= 0) continue;
+            const float* c = pr + a.cq_off;
+            AT* dst = (AT*)a.cq_out + (size_t)t * a.ld_cq;
+            float ss = 0.f;
+            for (int i = lane; i < a.q_rank; i += 32) ss = fmaf(c[i], c[i], ss);
+            ss = warp_sum(ss);
+            const float rs = 1.0f / sqrtf(ss / (float)a.q_rank + a.eps);
+            for (int i = lane; i < a.q_rank; i += 32) stv(dst + i, c[i] * rs * a.cq_gain[i]);
+        } else if (job == 0) {
+            if (!a.cache) continue;
             const float* c = pr + a.c_off;
             CT* dst = (CT*)a.cache + ((size_t)page * P3_PAGE + off) * (R + dr);
             float ss = 0.f;
@@ -432,13 +452,13 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
             const float* kr = c + R;
             for (int i = lane; i < half; i += 32) {
                 float ou, ov;
-                turn_pair(kr[i], kr[i + half], fpos * a.freq[i], a.rot_mag, ou, ov);
-                stv(dst + R + i, ou); stv(dst + R + half + i, ov);
+                turn_pair(kr[pa * i], kr[pa * i + pb], fpos * a.freq[i], a.rot_mag, ou, ov);
+                stv(dst + R + pa * i, ou); stv(dst + R + pa * i + pb, ov);
             }
             for (int i = a.rot_n + lane; i < dr; i += 32) stv(dst + R + i, kr[i]);
         } else {
             const int h = job - 1;
-            const float* q = pr + a.q_off + (size_t)h * (d + dr);
+            const float* q = (a.q_src ? a.q_src + (size_t)t * a.ld_qsrc : pr + a.q_off) + (size_t)h * (d + dr);
             AT* qp = (AT*)a.q_plain + (size_t)t * a.ld_qp + (size_t)h * d;
             for (int i = lane; i < d; i += 32) stv(qp + i, q[i]);
             if (dr > 0) {
@@ -446,8 +466,8 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
                 AT* ql = (AT*)a.q_lat + (size_t)t * a.ld_ql + (size_t)h * (R + dr) + R;
                 for (int i = lane; i < half; i += 32) {
                     float ou, ov;
-                    turn_pair(qr[i], qr[i + half], fpos * a.freq[i], a.rot_mag, ou, ov);
-                    stv(ql + i, ou); stv(ql + half + i, ov);
+                    turn_pair(qr[pa * i], qr[pa * i + pb], fpos * a.freq[i], a.rot_mag, ou, ov);
+                    stv(ql + pa * i, ou); stv(ql + pa * i + pb, ov);
                 }
                 for (int i = a.rot_n + lane; i < dr; i += 32) stv(ql + i, qr[i]);
             }
@@ -835,6 +855,51 @@ __global__ void moe_combine_identity_kernel(const float* __restrict__ y, int64_t
         out[(size_t)t * W + i] = s + (add ? add[(size_t)t * ld_add + i] : 0.f);
     }
 }
+// ---------------------------------------------------------------- embedding plus the row of a hashed (previous, current) token pair
+// One CTA per row. The token before a row is the row above it inside a sequence's run of rows, else the token the slot saved at
+// the end of the sequence's last step. The CTA of a sequence's first row reads the saved token and then replaces it by the
+// sequence's last token of this step (read, barrier, write), so no other CTA touches the slot's state.
+__global__ void embed_pair_rows_kernel(const bf16* __restrict__ table, const bf16* __restrict__ pair_table, const int32_t* __restrict__ ids,
+                                       const int32_t* __restrict__ seqs, const int32_t* __restrict__ slot_seq,
+                                       const int32_t* __restrict__ tok_slot, int32_t* prev_state, int64_t state_stride,
+                                       float* __restrict__ x, int W, int vocab, float scale, long long buckets, long long mul_prev,
+                                       long long mul_cur) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int64_t t = blockIdx.x;
+    int id = ids[t];
+    const int slot = tok_slot[t];
+    const int4 rec = reinterpret_cast<const int4*>(seqs)[slot_seq[slot]];   // {first row, rows, slot, first position}
+    const bool first = t == rec.x;
+    const long long prev = first ? (rec.w > 0 ? prev_state[(size_t)slot * state_stride] : -1) : ids[t - 1];
+    if (first) {
+        __syncthreads();                                     // every thread has read the saved token
+        if (threadIdx.x == 0) prev_state[(size_t)slot * state_stride] = ids[rec.x + rec.y - 1];
+    }
+    long long pr = buckets;                                  // a sequence's first token: the table's last row
+    if (prev >= 0) { pr = (prev * mul_prev + (long long)id * mul_cur) % buckets; if (pr < 0) pr += buckets; }
+    if (id < 0 || id >= vocab) id = 0;
+    const bf16* src = table + (size_t)id * W;
+    const bf16* ps = pair_table ? pair_table + (size_t)pr * W : nullptr;
+    for (int i0 = threadIdx.x; i0 < W; i0 += RPT * blockDim.x) {
+        float v[RPT], u[RPT];
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            const int i = i0 + k * blockDim.x;
+            v[k] = i < W ? __bfloat162float(src[i]) : 0.f;
+            u[k] = (ps && i < W) ? __bfloat162float(ps[i]) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < RPT; k++) { const int i = i0 + k * blockDim.x; if (i < W) x[(size_t)t * W + i] = v[k] * scale + u[k]; }
+    }
+}
+
+__global__ void distance_linear_kernel(const float* __restrict__ slope, float* __restrict__ pen, int H, int n) {
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= (int64_t)H * n) return;
+    const int h = (int)(i / n);
+    pen[i] = slope[h] * (float)(i - (int64_t)h * n);
+}
 }  // namespace
 
 extern "C" int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
@@ -960,12 +1025,16 @@ extern "C" int p3_residual_layernorm(float* x, const float* add1, int64_t ld1, c
 }
 
 extern "C" int p3_latent_post(const p3_latent_post_args* a, cudaStream_t st) {
-    P3_CHECK_ARG(a && a->proj && a->q_plain && a->cache && a->c_gain && a->block_table && a->tok_slot && a->tok_pos, "latent_post: null argument");
-    P3_CHECK_ARG(a->rot_dim == 0 || (a->q_lat && a->freq), "latent_post: a turning part needs q_lat and the frequencies");
+    P3_CHECK_ARG(a && a->block_table && a->tok_slot && a->tok_pos, "latent_post: null argument");
+    P3_CHECK_ARG(a->n_heads == 0 || ((a->proj || a->q_src) && a->q_plain), "latent_post: the query part needs its source and q_plain");
+    P3_CHECK_ARG(!a->cache || (a->proj && a->c_gain), "latent_post: the latent part needs proj and its gain");
+    P3_CHECK_ARG(a->q_rank <= 0 || (a->proj && a->cq_gain && a->cq_out), "latent_post: the query's low-rank vector needs proj, its gain and its output");
+    P3_CHECK_ARG(a->n_ff == 0 || a->proj, "latent_post: the gated unit reads proj");
+    P3_CHECK_ARG(a->rot_dim == 0 || a->rot_n == 0 || (a->freq && (a->n_heads == 0 || a->q_lat)), "latent_post: a turning part needs q_lat and the frequencies");
     P3_CHECK_ARG(a->rot_n >= 0 && a->rot_n <= a->rot_dim && a->rot_n % 2 == 0, "latent_post: rot_n must be even and <= rot_dim");
     P3_CHECK_ARG(a->n_ff == 0 || a->hid, "latent_post: the gated unit needs its output");
     if (a->T == 0) return 0;
-    const int jobs = 1 + a->n_heads, th = 128;
+    const int jobs = 2 + a->n_heads, th = 128;
     // few tokens: one warp per job and enough CTAs for the gated unit's columns; many tokens: one CTA per token
     int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
     if (a->T < 1024 && groups < (a->n_ff + 2047) / 2048) groups = (a->n_ff + 2047) / 2048;
@@ -1105,5 +1174,28 @@ extern "C" int p3_moe_combine_identity(const float* y, int64_t ldy, const int32_
     p3_launch_pdl(moe_combine_identity_kernel, dim3((unsigned)T), dim3(W >= 1024 ? 256 : 128), (size_t)(2 * top * sizeof(float)), st,
                   y, ldy, where, ids, wts, top, n_real, h, add, ld_add, out, W);
     P3_CHECK_LAUNCH("moe_combine_identity");
+    return 0;
+}
+
+extern "C" int p3_embed_pair_rows_f32(const void* table, const void* pair_table, const int32_t* ids, const int32_t* seqs,
+                                      const int32_t* slot_seq, const int32_t* tok_slot, int32_t* prev_state, int64_t state_stride,
+                                      float* x, int64_t T, int W, int vocab, float scale, int64_t buckets, int64_t mul_prev,
+                                      int64_t mul_cur, cudaStream_t st) {
+    P3_CHECK_ARG(table && ids && seqs && slot_seq && tok_slot && prev_state && x, "embed_pair_rows_f32: null argument");
+    P3_CHECK_ARG(((uintptr_t)seqs & 15) == 0, "embed_pair_rows_f32: the sequence records must be 16-byte aligned");
+    P3_CHECK_ARG(!pair_table || buckets >= 1, "embed_pair_rows_f32: the pair table needs at least one bucket");
+    if (T == 0) return 0;
+    if (!pair_table) buckets = 1;
+    p3_launch_pdl(embed_pair_rows_kernel, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, (const bf16*)pair_table, ids, seqs,
+                  slot_seq, tok_slot, prev_state, state_stride, x, W, vocab, scale, (long long)buckets, (long long)mul_prev, (long long)mul_cur);
+    P3_CHECK_LAUNCH("embed_pair_rows_f32");
+    return 0;
+}
+
+extern "C" int p3_distance_linear_table(const float* slope, float* pen, int H, int n, cudaStream_t st) {
+    P3_CHECK_ARG(slope && pen && H >= 1 && n >= 1, "distance_linear_table: bad argument");
+    const int64_t tot = (int64_t)H * n;
+    distance_linear_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(slope, pen, H, n);
+    P3_CHECK_LAUNCH("distance_linear_table");
     return 0;
 }

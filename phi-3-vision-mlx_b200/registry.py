@@ -107,8 +107,20 @@ def _dugalix_build(cfg, weights, device='cuda', dtype=None, **kw):
     return DugalixB200(cfg, weights, device=device, dtype=dtype or torch.bfloat16)
 
 
+def _danalorn_config(d):
+    from .configs import DanalornConfig
+    return DanalornConfig(d)
+
+
+def _danalorn_build(cfg, weights, device='cuda', dtype=None, **kw):
+    import torch
+    from .danalorn import DanalornB200
+    return DanalornB200(cfg, weights, device=device, dtype=dtype or torch.bfloat16)
+
+
 register('Phi3ForCausalLM', _phi3_config, _phi3_build, 'batch')
 register('Phi3VForCausalLM', _phi3_config, _phi3_build, 'batch')
 register('Tagenex', _tagenex_config, _tagenex_build, 'paged')
 register('Tapalix', _tapalix_config, _tapalix_build, 'paged')
 register('Dugalix', _dugalix_config, _dugalix_build, 'paged')
+register('Danalorn', _danalorn_config, _danalorn_build, 'paged')

@@ -294,3 +294,72 @@ def random_dugalix_weights(cfg, seed=0, device='cpu'):
             t = rn(shape) / shape[-1] ** 0.5
         w[name] = t.to(torch.bfloat16)
     return w
+
+
+def danalorn_tensor_shapes(cfg):
+    """name -> shape of every tensor of a Danalorn checkpoint; cfg = the config.json dict"""
+    W, V = cfg['width'], cfg['vocab']
+    out = {'embed': (V, W)}
+    bg = (cfg.get('embedding') or {}).get('bigram')
+    if bg:
+        out['bigram'] = (bg['buckets'] + 1, W)
+    for i, lc in enumerate(cfg['layers']):
+        p, m = f'l{i}.', lc['mixer']
+        a = p + 'mix.'
+        out.update({p + 'norm1': (W,), p + 'norm1b': (W,)})
+        if lc['type'] == 'latent_attention':
+            H, d, dr, R, Q = m['heads'], m['dim'], m.get('rot_dim', 0), m['kv_rank'], m['q_rank']
+            dv = m.get('vdim', d)
+            out.update({a + 'dq': (Q, W), a + 'dq.norm': (Q,), a + 'uq': (H * (d + dr), Q)})
+            if m.get('kv_from') is None:
+                out.update({a + 'dkv': (R + dr, W), a + 'dkv.norm': (R,)})
+            out.update({a + 'uk': (H * d, R), a + 'uv': (H * dv, R), a + 'sink': (H,), a + 'o': (W, H * dv)})
+        elif lc['type'] == 'attention':
+            H, G, d = m['heads'], m.get('kv_heads', m['heads']), m['dim']
+            dv = m.get('vdim', d)
+            out.update({a + 'q': (H * d, W), a + 'q.b': (H * d,), a + 'k': (G * d, W), a + 'k.b': (G * d,), a + 'v': (G * dv, W),
+                        a + 'v.b': (G * dv,), a + 'q.norm': (d,), a + 'k.norm': (d,), a + 'g': (H * dv, W), a + 'o': (W, H * dv)})
+        elif lc['type'] == 'gla':
+            H, d = m['heads'], m['dim']
+            dv = m.get('vdim', d)
+            r = m.get('decay_rank', 16)          # checkpoints fix this by the shape of a1; random ones take 16 unless told otherwise
+            out.update({a + 'q': (H * d, W), a + 'k': (H * d, W), a + 'v': (H * dv, W), a + 'g': (H * dv, W), a + 'o': (W, H * dv),
+                        a + 'norm': (dv,), a + 'a1': (r, W), a + 'a2': (H * d, r), a + 'a2.b': (H * d,)})
+        else:
+            raise NotImplementedError(lc['type'])
+        f = lc.get('mlp')
+        if f is not None:
+            out.update({p + 'norm2': (W,), p + 'norm2b': (W,), p + 'mlp.up': (f['ff'], W), p + 'mlp.down': (W, f['ff'])})
+    out.update({'final.norm': (W,), 'head': (V, W)})
+    return out
+
+
+def random_danalorn_weights(cfg, seed=0, device='cpu'):
+    """Seeded bf16 tensors for a Danalorn config dict: matrices N(0, 1/fan_in), embedding and pair table of unit spread (the pair
+    table weighs as much as a scaled token row would not: it has to show beside it, so its spread is that of the scaled rows),
+    norm gains around one, biases 0.1 N except the decay biases of the recurrence (around 3 +- 2: decays from a few tokens to
+    hundreds), sinks N(0, 1)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda s: torch.randn(s, generator=g, device=device, dtype=torch.float32)
+    scale = float((cfg.get('embedding') or {}).get('scale', 1.0))
+    w = {}
+    for name, shape in danalorn_tensor_shapes(cfg).items():
+        leaf = name.split('.', 1)[1] if name.startswith('l') and name[1].isdigit() else name
+        if leaf == 'mix.a2.b':
+            t = 3.0 + 2.0 * rn(shape)
+        elif leaf == 'mix.a2':
+            t = 2.0 * rn(shape) / shape[-1] ** 0.5
+        elif leaf.endswith('.b'):
+            t = 0.1 * rn(shape)
+        elif leaf == 'embed':
+            t = rn(shape)
+        elif leaf == 'bigram':
+            t = rn(shape) * scale
+        elif leaf == 'mix.sink':
+            t = rn(shape)
+        elif 'norm' in leaf.rsplit('.', 1)[-1]:
+            t = 1.0 + 0.1 * rn(shape)
+        else:
+            t = rn(shape) / shape[-1] ** 0.5
+        w[name] = t.to(torch.bfloat16)
+    return w
