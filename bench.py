@@ -761,6 +761,75 @@ def run_dugalix(args):
           'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
 
 
+# ------------------------------------------------------------------------------------------------ --arch danalorn
+def _danalorn_cfg(width, heads, kv, dim, lat_dim, lat_rot, rank, q_rank, window, gh, gdim, gvdim, ff, layers, vocab):
+    lat = {'type': 'latent_attention',
+           'mixer': {'heads': heads, 'dim': lat_dim, 'rot_dim': lat_rot, 'vdim': lat_dim, 'kv_rank': rank, 'q_rank': q_rank,
+                     'scale': (lat_dim + lat_rot) ** -0.5, 'mask': {'size': window}, 'rot': {'base': 500000.0, 'dims': lat_rot}}}
+    att = {'type': 'attention', 'mixer': {'heads': heads, 'kv_heads': kv, 'dim': dim, 'vdim': dim, 'scale': dim ** -0.5,
+                                          'q_temp': {'coef': 0.3, 'every': 64}}}
+    gla = {'type': 'gla', 'mixer': {'heads': gh, 'dim': gdim, 'vdim': gvdim, 'tau': 16.0}}
+    order = [lat, att, gla, gla]
+    return {'architecture': 'Danalorn', 'vocab': vocab, 'width': width, 'norm': {'eps': 1e-5},
+            'embedding': {'scale': width ** 0.5, 'bigram': {'buckets': 65521, 'mul_prev': 31, 'mul_cur': 7}},
+            'layers': [dict(order[i % 4], mlp={'kind': 'dense', 'ff': ff}) for i in range(layers)]}
+
+
+def run_danalorn(args):
+    """Throughput of the Danalorn design on the continuous-batching engine at layer sizes of a real model (random weights, bf16
+    serving mode), beside Dugalix, the closest existing model (same engine, page pool with state rows, sandwich norms, relu^2 units,
+    product kernels, attention kernels and a recurrent scan of the same layout), at equal width, depth, attention shape, recurrent
+    state shape and feed-forward size. One JSON line: per size the prefill and decode tok/s of both and, per kernel family, time and
+    achieved FLOP/s (prefill) or bytes/s (decode) against the measured peaks."""
+    import torch
+    import phi3_b200  # noqa: F401
+    from phi3_b200 import weights
+    from phi3_b200.dugalix import DugalixB200
+    from phi3_b200.danalorn import DanalornB200
+    hbm, _ = peaks()
+    tf = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json'))).get('bf16_tflops', 1590.0) if os.path.exists(
+        os.path.join(ROOT, 'MEASURED_PEAKS.json')) else 1590.0
+    dev = torch.device('cuda:0')
+    sizes = [dict(name='w2048_h16x128_kv4_lat(64+32)r96_g8x128x256_ff8192_L4', width=2048, heads=16, kv=4, dim=128, lat_dim=64,
+                  lat_rot=32, rank=96, q_rank=768, window=1024, gh=8, gdim=128, gvdim=256, ff=8192, layers=4),
+             dict(name='w2048_h16x128_kv4_lat(64+32)r96_g8x128x256_ff8192_L4_b16', width=2048, heads=16, kv=4, dim=128, lat_dim=64,
+                  lat_rot=32, rank=96, q_rank=768, window=1024, gh=8, gdim=128, gvdim=256, ff=8192, layers=4, batch=16),
+             dict(name='w3072_h32x64_kv8_lat(64+32)r96_g12x64x256_ff8192_L4', width=3072, heads=32, kv=8, dim=64, lat_dim=64,
+                  lat_rot=32, rank=96, q_rank=1024, window=512, gh=12, gdim=64, gvdim=256, ff=8192, layers=4)]
+    if getattr(args, 'sizes', None):
+        sizes = [sz for i, sz in enumerate(sizes) if str(i) in args.sizes.split(',')]
+    vocab, L, CTX_D, NEW_D = 32064, 2048, 2048, 32
+    out = []
+    for sz in sizes:
+        B = sz.get('batch', 4)
+        cfg = _danalorn_cfg(sz['width'], sz['heads'], sz['kv'], sz['dim'], sz['lat_dim'], sz['lat_rot'], sz['rank'], sz['q_rank'],
+                            sz['window'], sz['gh'], sz['gdim'], sz['gvdim'], sz['ff'], sz['layers'], vocab)
+        m = DanalornB200(cfg, weights.random_danalorn_weights(cfg, 0, device=dev), dtype=torch.bfloat16)
+        _, nums = _engine_model_numbers(m, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+        row = dict(size=sz['name'], batch=B, prompt=L, danalorn=nums)
+        del m
+        torch.cuda.empty_cache()
+        # Dugalix at equal size: windowed attention of the same shape in every layer, a matrix memory of the recurrent state's shape
+        # in every other layer, the same dense unit
+        rot = lambda dims, factor=None: {'base': 500000.0, 'dims': dims, **({'scaling': {'factor': factor}} if factor else {})}
+        par = {'type': 'parallel',
+               'mixer': {'left': {'heads': sz['heads'], 'kv_heads': sz['kv'], 'dim': sz['dim'], 'vdim': sz['dim'], 'scale': sz['dim'] ** -0.5,
+                                  'mask': {'size': sz['window'], 'keep_first': 64}, 'rot': rot(sz['dim'], 4.0)},
+                         'right': {'heads': sz['gh'], 'dim': sz['gdim'], 'vdim': sz['gvdim'], 'gate_cap': 15.0},
+                         'left_scale': 0.7, 'right_scale': 0.7}}
+        sig = {'type': 'attention', 'mixer': {'heads': sz['heads'], 'kv_heads': sz['kv'], 'dim': sz['dim'], 'vdim': sz['dim'],
+                                              'scale': sz['dim'] ** -0.5, 'mask': {'size': sz['window']}, 'rot': rot(sz['dim'] // 2)}}
+        dcfg = {'architecture': 'Dugalix', 'vocab': vocab, 'width': sz['width'], 'norm': {'eps': 1e-5}, 'residual_mult': 0.6,
+                'layers': [dict(sig if i % 2 else par, mlp={'kind': 'dense', 'ff': sz['ff']}) for i in range(sz['layers'])]}
+        dm = DugalixB200(dcfg, weights.random_dugalix_weights(dcfg, 0, device=dev), dtype=torch.bfloat16)
+        _, row['dugalix_equal_size'] = _engine_model_numbers(dm, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+        del dm
+        torch.cuda.empty_cache()
+        out.append(row)
+    _emit({"metric": "danalorn_prefill_decode_tok_per_s", 'arch': 'danalorn', 'dtype': 'bf16', 'data': 'synthetic', 'n_gpus': 1,
+          'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -768,10 +837,10 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex', 'tapalix', 'dugalix'],
-                    help='phi3: the headline workload (default); tagenex / tapalix / dugalix: prefill / decode throughput of that '
-                         'design on the continuous-batching engine, beside the closest existing model at equal size')
-    ap.add_argument('--sizes', default='', help='with --arch dugalix: indices of the sizes to run, with commas (default: all)')
+    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex', 'tapalix', 'dugalix', 'danalorn'],
+                    help='phi3: the headline workload (default); tagenex / tapalix / dugalix / danalorn: prefill / decode throughput of '
+                         'that design on the continuous-batching engine, beside the closest existing model at equal size')
+    ap.add_argument('--sizes', default='', help='with --arch dugalix / danalorn: indices of the sizes to run, with commas (default: all)')
     args = ap.parse_args()
     if not (args.gpus > 1 and int(os.environ.get('WORLD_SIZE', 1)) == 1):      # the self-launching parent just relays its child
         _claim_stdout()
@@ -783,6 +852,8 @@ def main():
         return run_tapalix(args)
     if args.arch == 'dugalix':
         return run_dugalix(args)
+    if args.arch == 'danalorn':
+        return run_danalorn(args)
     world = int(os.environ.get('WORLD_SIZE', 1))
     if args.gpus > 1 and world == 1:
         # convenience: self-launch under torchrun when called directly with --gpus N
