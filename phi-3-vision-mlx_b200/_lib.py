@@ -279,4 +279,5 @@ class GlaArgs(C.Structure):
     _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('k_off', C.c_int32), ('v_off', C.c_int32),
                 ('z', _p), ('ld_z', _l), ('z_bias', _p), ('inv_tau', C.c_float),
                 ('n_heads', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('q_scale', C.c_float),
-                ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l), ('rs_force', C.c_int32)]
+                ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l), ('rs_force', C.c_int32),
+                ('n_rows', C.c_int32)]

@@ -30,11 +30,11 @@
 // Gated linear attention (Yang et al., "Gated Linear Attention Transformers with Hardware-Efficient Training"). Per head a state
 // S [dim][vdim] that starts at zero, with one decay per key channel and token:
 //     S_t = diag(a_t) S_(t-1) + k_t v_t^T        y_t = S_t^T q_t        a_t = sigmoid(z_t)^(1/tau) = exp(logsigmoid(z_t) / tau)
+//   gla_decay_kernel            decay logits of all rows of the step -> decays, in place (one pass at memory speed)
 //   gla_scan_kernel             the matrix-memory scan's layout (columns of S in registers, rounds of staged tokens, async copies one
-//                               round ahead) with a staged row of decays beside every k and q row; the two helper warps turn the
-//                               decay logits of the next round into decays while the main warps work on this one. There is no
-//                               normaliser and no stabiliser: every factor is in (0, 1]. As there, a token's arithmetic does not
-//                               depend on how the sequence was cut into steps.
+//                               round ahead) with a staged row of decays beside every k and q row. There is no normaliser and no
+//                               stabiliser (every factor is in (0, 1]), so all four warps own columns. As there, a token's
+//                               arithmetic does not depend on how the sequence was cut into steps.
 #include "common.cuh"
 #include "../../include/phi3_b200.h"
 #include <cfloat>
@@ -243,13 +243,40 @@ __global__ void __launch_bounds__(MM_WARPS * 32) matrix_memory_scan_kernel(p3_ma
 
 __host__ __device__ inline int64_t gla_head_floats(int dim, int vdim) { return (int64_t)dim * vdim; }
 
+// decay logits -> decays, in place: z <- exp(logsigmoid(z + bias) * inv_tau), n numbers per row
+__global__ void gla_decay_kernel(float* __restrict__ z, int64_t ld_z, const float* __restrict__ bias, int64_t T, int n, float inv_tau, int vec) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int64_t step = (int64_t)gridDim.x * blockDim.x, me = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (vec) {
+        const int nq = n / 4;
+        for (int64_t i = me; i < T * nq; i += step) {
+            const int64_t t = i / nq;
+            const int c = (int)(i - t * nq) * 4;
+            float4 v = *reinterpret_cast<float4*>(z + t * ld_z + c);
+            const float4 b = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x = expf(log_sigmoid(v.x + b.x) * inv_tau); v.y = expf(log_sigmoid(v.y + b.y) * inv_tau);
+            v.z = expf(log_sigmoid(v.z + b.z) * inv_tau); v.w = expf(log_sigmoid(v.w + b.w) * inv_tau);
+            *reinterpret_cast<float4*>(z + t * ld_z + c) = v;
+        }
+    } else {
+        for (int64_t i = me; i < T * n; i += step) {
+            const int64_t t = i / n;
+            const int c = (int)(i - t * n);
+            z[t * ld_z + c] = expf(log_sigmoid(z[t * ld_z + c] + (bias ? bias[c] : 0.f)) * inv_tau);
+        }
+    }
+}
+
+constexpr int GLA_WARPS = 4;     // every warp owns columns of S
+
 template <int DS, int RS, int NC, int TB>
-__global__ void __launch_bounds__(MM_WARPS * 32) gla_scan_kernel(p3_gla_args a) {
+__global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(p3_gla_args a) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     // a warp = RS row slices x CW lanes, every lane with NC columns (CW apart); DP: dim rounded up
-    constexpr int CW = 32 / RS, WCOLS = CW * NC, COLS = MM_MAIN * WCOLS, DP = DS * RS;
-    constexpr int NT = MM_WARPS * 32, NH = NT - MM_MAIN * 32;   // all threads; threads of the helper warps
+    constexpr int CW = 32 / RS, WCOLS = CW * NC, COLS = GLA_WARPS * WCOLS, DP = DS * RS;
+    constexpr int NT = GLA_WARPS * 32;
     constexpr int DPP = DP + 4 * RS;                         // pitch of a staged row: its RS slices 4 floats apart (bank spread)
     constexpr int ROUND = TB * (3 * DPP + COLS);             // floats of one staged round
     auto at_row = [](int c) { return c + 4 * (c / DS); };    // where number c of a row lives
@@ -259,31 +286,32 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gla_scan_kernel(p3_gla_args a) 
     const int4 rec = reinterpret_cast<const int4*>(a.seqs)[blockIdx.x];
     const int row0 = rec.x, n_tok = rec.y, slot = rec.z, pos0 = rec.w;
     const int hd = blockIdx.y, vb = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool fresh = pos0 == 0, main = warp < MM_MAIN;
+    const bool fresh = pos0 == 0;
     float* Sg = a.state + ((size_t)slot * H + hd) * gla_head_floats(d, dv);
     const int col = vb * COLS + warp * WCOLS + lane % CW, d0 = (lane / CW) * DS;   // first of this lane's columns
     float S[NC][DS];
-    if (main) {
 #pragma unroll
-        for (int c = 0; c < NC; c++)
+    for (int c = 0; c < NC; c++)
 #pragma unroll
-            for (int j = 0; j < DS; j++)
-                S[c][j] = (!fresh && col + c * CW < dv && d0 + j < d) ? Sg[(size_t)(d0 + j) * dv + col + c * CW] : 0.f;
-    }
-    const bool vec = d % 4 == 0 && a.ld_proj % 4 == 0 && a.q_off % 4 == 0 && a.k_off % 4 == 0 && ((uintptr_t)a.proj & 15) == 0;
+        for (int j = 0; j < DS; j++)
+            S[c][j] = (!fresh && col + c * CW < dv && d0 + j < d) ? Sg[(size_t)(d0 + j) * dv + col + c * CW] : 0.f;
+    const bool vec = d % 4 == 0 && a.ld_proj % 4 == 0 && a.q_off % 4 == 0 && a.k_off % 4 == 0 && ((uintptr_t)a.proj & 15) == 0 &&
+                     a.ld_z % 4 == 0 && ((uintptr_t)a.z & 15) == 0;
 
-    // all threads: start the copies of the round that begins at token t0 into buffer `buf`
+    // all threads: start the copies of the round that begins at token t0 into buffer `buf` (q is scaled when the sums are written)
     auto stage = [&](int t0, int buf) {
         const int nb = min(TB, n_tok - t0);
         float* qs = sm + buf * ROUND;
         float* ks = qs + TB * DPP;
-        float* vs = ks + 2 * TB * DPP;
+        float* as = ks + TB * DPP;
+        float* vs = as + TB * DPP;
         if (vec) {
             for (int i = tid; i < nb * (DP / 4); i += NT) {
                 const int tt = i / (DP / 4), c = (i - tt * (DP / 4)) * 4;
                 const float* pr = a.proj + (size_t)(row0 + t0 + tt) * a.ld_proj + (size_t)hd * d + (c < d ? c : 0);
                 cp_async16(smem_u32(qs + tt * DPP + at_row(c)), pr + a.q_off, c < d ? 16 : 0);
                 cp_async16(smem_u32(ks + tt * DPP + at_row(c)), pr + a.k_off, c < d ? 16 : 0);
+                cp_async16(smem_u32(as + tt * DPP + at_row(c)), a.z + (size_t)(row0 + t0 + tt) * a.ld_z + (size_t)hd * d + (c < d ? c : 0), c < d ? 16 : 0);
             }
         } else {
             for (int i = tid; i < nb * DP; i += NT) {
@@ -291,6 +319,7 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gla_scan_kernel(p3_gla_args a) 
                 const float* pr = a.proj + (size_t)(row0 + t0 + tt) * a.ld_proj + (size_t)hd * d + (c < d ? c : 0);
                 cp_async4z(smem_u32(qs + tt * DPP + at_row(c)), pr + a.q_off, c < d ? 4 : 0);
                 cp_async4z(smem_u32(ks + tt * DPP + at_row(c)), pr + a.k_off, c < d ? 4 : 0);
+                cp_async4z(smem_u32(as + tt * DPP + at_row(c)), a.z + (size_t)(row0 + t0 + tt) * a.ld_z + (size_t)hd * d + (c < d ? c : 0), c < d ? 4 : 0);
             }
         }
         for (int i = tid; i < nb * COLS; i += NT) {
@@ -298,82 +327,56 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gla_scan_kernel(p3_gla_args a) 
             cp_async4z(smem_u32(vs + i), a.proj + (size_t)(row0 + t0 + tt) * a.ld_proj + a.v_off + (size_t)hd * dv + (c < dv ? c : 0), c < dv ? 4 : 0);
         }
     };
-    // helper warps: the decays of the round, exp(logsigmoid(z + bias) / tau), four independent numbers per thread and pass
-    auto decays = [&](int t0, int buf) {
-        const int nb = min(TB, n_tok - t0), me = tid - MM_MAIN * 32;
-        float* as = sm + buf * ROUND + 2 * TB * DPP;
-        for (int i0 = me; i0 < nb * DP; i0 += 4 * NH) {
-            float z[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = i0 + u * NH, tt = i / DP, c = i - tt * DP;
-                z[u] = (i < nb * DP && c < d) ? a.z[(size_t)(row0 + t0 + tt) * a.ld_z + (size_t)hd * d + c] + (a.z_bias ? a.z_bias[hd * d + c] : 0.f)
-                                              : 0.f;
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = i0 + u * NH, tt = i / DP, c = i - tt * DP;
-                if (i < nb * DP) as[tt * DPP + at_row(c)] = c < d ? expf(log_sigmoid(z[u]) * a.inv_tau) : 0.f;
-            }
-        }
-    };
 
     stage(0, 0);
     cp_async_commit();
-    if (!main) decays(0, 0);
     for (int t0 = 0, r = 0; t0 < n_tok; t0 += TB, r++) {
         const int nb = min(TB, n_tok - t0), buf = r & 1;
         cp_async_wait<0>();                                  // this thread's copies of round r have landed ...
-        __syncthreads();                                     // ... and everyone's, with the round's decays; round r - 1 is consumed
+        __syncthreads();                                     // ... and everyone's; round r - 1 is consumed
         if (t0 + TB < n_tok) stage(t0 + TB, buf ^ 1);
         cp_async_commit();
         const float* qs = sm + buf * ROUND;
         const float* ks = qs + TB * DPP;
         const float* as = ks + TB * DPP;
         const float* vs = as + TB * DPP;
-        if (main) {
-#pragma unroll 2
-            for (int tt = 0; tt < nb; tt++) {
-                float tv[NC], acc[NC][4];
+#pragma unroll(DS >= 128 ? 1 : 2)
+        for (int tt = 0; tt < nb; tt++) {
+            float tv[NC], acc[NC][4];
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                tv[c] = vs[tt * COLS + warp * WCOLS + lane % CW + c * CW];
+                acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+            }
+            const float4* kq = reinterpret_cast<const float4*>(ks + tt * DPP + at_row(d0));
+            const float4* qq = reinterpret_cast<const float4*>(qs + tt * DPP + at_row(d0));
+            const float4* aq = reinterpret_cast<const float4*>(as + tt * DPP + at_row(d0));
+#pragma unroll
+            for (int j = 0; j < DS; j += 4) {
+                const float4 kk = kq[j / 4], qv = qq[j / 4], al = aq[j / 4];
 #pragma unroll
                 for (int c = 0; c < NC; c++) {
-                    tv[c] = vs[tt * COLS + warp * WCOLS + lane % CW + c * CW];
-                    acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
-                }
-                const float4* kq = reinterpret_cast<const float4*>(ks + tt * DPP + at_row(d0));
-                const float4* qq = reinterpret_cast<const float4*>(qs + tt * DPP + at_row(d0));
-                const float4* aq = reinterpret_cast<const float4*>(as + tt * DPP + at_row(d0));
-#pragma unroll
-                for (int j = 0; j < DS; j += 4) {
-                    const float4 kk = kq[j / 4], qv = qq[j / 4], al = aq[j / 4];
-#pragma unroll
-                    for (int c = 0; c < NC; c++) {
-                        S[c][j] = fmaf(kk.x, tv[c], al.x * S[c][j]);         acc[c][0] = fmaf(S[c][j], qv.x, acc[c][0]);
-                        S[c][j + 1] = fmaf(kk.y, tv[c], al.y * S[c][j + 1]); acc[c][1] = fmaf(S[c][j + 1], qv.y, acc[c][1]);
-                        S[c][j + 2] = fmaf(kk.z, tv[c], al.z * S[c][j + 2]); acc[c][2] = fmaf(S[c][j + 2], qv.z, acc[c][2]);
-                        S[c][j + 3] = fmaf(kk.w, tv[c], al.w * S[c][j + 3]); acc[c][3] = fmaf(S[c][j + 3], qv.w, acc[c][3]);
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < NC; c++) {
-                    float y = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
-                    if (RS >= 2) y += __shfl_xor_sync(0xffffffffu, y, CW);
-                    if (RS >= 4) y += __shfl_xor_sync(0xffffffffu, y, 2 * CW);
-                    if (lane < CW && col + c * CW < dv)
-                        a.out[(size_t)(row0 + t0 + tt) * a.ld_out + (size_t)hd * dv + col + c * CW] = y * a.q_scale;
+                    S[c][j] = fmaf(kk.x, tv[c], al.x * S[c][j]);         acc[c][0] = fmaf(S[c][j], qv.x, acc[c][0]);
+                    S[c][j + 1] = fmaf(kk.y, tv[c], al.y * S[c][j + 1]); acc[c][1] = fmaf(S[c][j + 1], qv.y, acc[c][1]);
+                    S[c][j + 2] = fmaf(kk.z, tv[c], al.z * S[c][j + 2]); acc[c][2] = fmaf(S[c][j + 2], qv.z, acc[c][2]);
+                    S[c][j + 3] = fmaf(kk.w, tv[c], al.w * S[c][j + 3]); acc[c][3] = fmaf(S[c][j + 3], qv.w, acc[c][3]);
                 }
             }
-        } else {
-            if (t0 + TB < n_tok) decays(t0 + TB, buf ^ 1);    // the next round's decays, while the main warps work on this one
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                float y = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
+                if (RS >= 2) y += __shfl_xor_sync(0xffffffffu, y, CW);
+                if (RS >= 4) y += __shfl_xor_sync(0xffffffffu, y, 2 * CW);
+                if (lane < CW && col + c * CW < dv)
+                    a.out[(size_t)(row0 + t0 + tt) * a.ld_out + (size_t)hd * dv + col + c * CW] = y * a.q_scale;
+            }
         }
     }
-    if (main) {
 #pragma unroll
-        for (int c = 0; c < NC; c++)
+    for (int c = 0; c < NC; c++)
 #pragma unroll
-            for (int j = 0; j < DS; j++)
-                if (col + c * CW < dv && d0 + j < d) Sg[(size_t)(d0 + j) * dv + col + c * CW] = S[c][j];
-    }
+        for (int j = 0; j < DS; j++)
+            if (col + c * CW < dv && d0 + j < d) Sg[(size_t)(d0 + j) * dv + col + c * CW] = S[c][j];
 }
 
 // one warp per (token, head)
@@ -481,7 +484,15 @@ extern "C" int p3_gla_scan(const p3_gla_args* a, cudaStream_t st) {
     P3_CHECK_ARG(a && a->proj && a->z && a->state && a->seqs && a->out, "gla_scan: null argument");
     P3_CHECK_ARG(a->n_heads >= 1 && a->dim >= 1 && a->dim <= 512 && a->vdim >= 1, "gla_scan: need heads >= 1, 1 <= dim <= 512, vdim >= 1");
     P3_CHECK_ARG(((uintptr_t)a->seqs & 15) == 0, "gla_scan: the sequence records must be 16-byte aligned");
-    if (a->n_seqs == 0) return 0;
+    P3_CHECK_ARG(a->n_rows >= 0, "gla_scan: the number of rows must not be negative");
+    if (a->n_seqs == 0 || a->n_rows == 0) return 0;
+    {   // decays first, over all rows of the step at once and in place: the scan then stages them like k and q
+        const int n = a->n_heads * a->dim;
+        const int vec = n % 4 == 0 && a->ld_z % 4 == 0 && ((uintptr_t)a->z & 15) == 0 && (!a->z_bias || ((uintptr_t)a->z_bias & 15) == 0);
+        const int64_t work = (int64_t)a->n_rows * (vec ? n / 4 : n);
+        const unsigned blocks = (unsigned)(work + 255) / 256 < 148u * 8 ? (unsigned)((work + 255) / 256) : 148u * 8;
+        p3_launch_pdl(gla_decay_kernel, dim3(blocks ? blocks : 1), dim3(256), (size_t)(0), st, a->z, a->ld_z, a->z_bias, (int64_t)a->n_rows, n, a->inv_tau, vec);
+    }
     // the shape of a warp as for the matrix memory: four row slices x eight lanes, two columns per lane when that still leaves a
     // CTA for every SM
     int rs = 4, nc = (int64_t)a->n_seqs * a->n_heads * ((a->vdim + 63) / 64) >= 148 ? 2 : 1;
@@ -489,15 +500,15 @@ extern "C" int p3_gla_scan(const p3_gla_args* a, cudaStream_t st) {
     if (a->rs_force == 8) { rs = 4; nc = 2; }
     if (a->dim > 256) { rs = 4; nc = 1; }                    // 128 rows per thread, 16 tokens per round
     const int per = (a->dim + rs - 1) / rs, ds = per <= 16 ? 16 : per <= 32 ? 32 : per <= 64 ? 64 : 128;
-    const int cols = MM_MAIN * 32 / rs * nc, tb = a->dim > 256 ? 16 : MM_TB;
+    const int cols = GLA_WARPS * 32 / rs * nc, tb = a->dim > 256 ? 16 : MM_TB;
     const dim3 grid((unsigned)a->n_seqs, (unsigned)a->n_heads, (unsigned)((a->vdim + cols - 1) / cols));
     const size_t bytes = sizeof(float) * (size_t)2 * tb * (3 * (ds * rs + 4 * rs) + cols);   // two staged rounds
 #define GO(DS, RS, NC)                                                                                              \
     do { if (set_smem_attr(gla_scan_kernel<DS, RS, NC, MM_TB>, bytes)) return -1;                                     \
-         p3_launch_pdl(gla_scan_kernel<DS, RS, NC, MM_TB>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a); } while (0)
+         p3_launch_pdl(gla_scan_kernel<DS, RS, NC, MM_TB>, dim3(grid), dim3(GLA_WARPS * 32), (size_t)(bytes), st, *a); } while (0)
     if (a->dim > 256) {
         if (set_smem_attr(gla_scan_kernel<128, 4, 1, 16>, bytes)) return -1;
-        p3_launch_pdl(gla_scan_kernel<128, 4, 1, 16>, dim3(grid), dim3(MM_WARPS * 32), (size_t)(bytes), st, *a);
+        p3_launch_pdl(gla_scan_kernel<128, 4, 1, 16>, dim3(grid), dim3(GLA_WARPS * 32), (size_t)(bytes), st, *a);
     } else if (rs == 2) { if (ds == 16) GO(16, 2, 1); else if (ds == 32) GO(32, 2, 1); else if (ds == 64) GO(64, 2, 1); else GO(128, 2, 1); }
     else if (nc == 1) { if (ds == 16) GO(16, 4, 1); else if (ds == 32) GO(32, 4, 1); else GO(64, 4, 1); }
     else { if (ds == 16) GO(16, 4, 2); else if (ds == 32) GO(32, 4, 2); else GO(64, 4, 2); }

@@ -27,8 +27,8 @@ Kernels per layer (csrc/): p3_embed_pair_rows_f32 -> p3_postnorm_prenorm ->
              _decode (window, sink) -> per-head value up-projection -> output product
   attention: ONE product [q | k | v | gate] -> p3_qkv_post (biases, head norms, query temperature, paged K/V write) ->
              p3_attn_window_prefill / _decode (distance table, unit sink, element-wise gate in the epilogue) -> output product
-  gla:       ONE product [q | k | v | gate] + decay down product -> decay up product -> p3_gla_scan -> p3_headnorm_gate_x -> output
-             product
+  gla:       ONE product [q | k | v | gate] + decay down product -> decay up product -> p3_gla_scan (decays in place, then the
+             scan) -> p3_headnorm_gate_x -> output product
 -> p3_postnorm_prenorm -> up product -> p3_relu2 -> down product -> p3_postnorm_prenorm.
 
 Precision. dtype=bfloat16 (serving): matrices, activations that feed a matrix product and the caches are bf16, accumulation is fp32;
@@ -356,7 +356,7 @@ class DanalornB200(PagedLM):
         r.z, r.ld_z, r.z_bias, r.inv_tau = ptr(z), z.stride(0), ptr(L['a2_b']), 1.0 / m.tau
         r.n_heads, r.dim, r.vdim, r.q_scale = H, d, dv, d ** -0.5
         r.state, r.seqs, r.n_seqs = ptr(pool.state[L['state']]), ptr(b.seqs), b.n_seq
-        r.out, r.ld_out = ptr(y), y.stride(0)
+        r.out, r.ld_out, r.n_rows = ptr(y), y.stride(0), T
         ev = self._ev()
         call_struct('p3_gla_scan', r, st)
         self._ev(ev, 'gla_scan', 4 * T * H * d * dv, T * (3 * H * d + 2 * H * dv) * 4)

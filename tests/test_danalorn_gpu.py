@@ -771,7 +771,7 @@ def test_gla_scan_in_portions_and_with_decays_at_both_ends(lib, shape, tau, rs):
             a.proj, a.ld_proj, a.q_off, a.k_off, a.v_off = ptr(pd), cols, off['q'], off['k'], off['v']
             a.z, a.ld_z, a.z_bias, a.inv_tau = ptr(zd), H * d, ptr(zbd), 1.0 / tau
             a.n_heads, a.dim, a.vdim, a.q_scale = H, d, dv, d ** -0.5
-            a.state, a.seqs, a.n_seqs, a.out, a.ld_out, a.rs_force = ptr(state), ptr(sq), len(seqs), ptr(y), H * dv, rs
+            a.state, a.seqs, a.n_seqs, a.out, a.ld_out, a.rs_force, a.n_rows = ptr(state), ptr(sq), len(seqs), ptr(y), H * dv, rs, r0
             call_struct('p3_gla_scan', a, 0)
             call('p3_headnorm_gate_x', ptr(y), H * dv, None, H, dv, ptr(gd), 1, ptr(pd[:, off['g']:]), cols, 1, 1.0, 1e-6, ptr(out),
                  H * dv, 1, r0, 0)
