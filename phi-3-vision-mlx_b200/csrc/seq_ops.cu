@@ -881,6 +881,23 @@ __global__ void embed_pair_rows_kernel(const bf16* __restrict__ table, const bf1
     if (id < 0 || id >= vocab) id = 0;
     const bf16* src = table + (size_t)id * W;
     const bf16* ps = pair_table ? pair_table + (size_t)pr * W : nullptr;
+    if (W % 8 == 0 && (((uintptr_t)table | (uintptr_t)pair_table | (uintptr_t)x) & 15) == 0) {   // eight numbers per thread and pass
+        for (int i = threadIdx.x * 8; i < W; i += 8 * blockDim.x) {
+            const uint4 a = *reinterpret_cast<const uint4*>(src + i);
+            const uint4 b = ps ? *reinterpret_cast<const uint4*>(ps + i) : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+            float o[8];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {                    // a bf16 is the upper half of its fp32
+                o[2 * k] = __uint_as_float(aw[k] << 16) * scale + __uint_as_float(bw[k] << 16);
+                o[2 * k + 1] = __uint_as_float(aw[k] & 0xffff0000u) * scale + __uint_as_float(bw[k] & 0xffff0000u);
+            }
+            float4* dst = reinterpret_cast<float4*>(x + (size_t)t * W + i);
+            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+        }
+        return;
+    }
     for (int i0 = threadIdx.x; i0 < W; i0 += RPT * blockDim.x) {
         float v[RPT], u[RPT];
 #pragma unroll

@@ -586,10 +586,11 @@ def test_window_sizes_around_a_page(lib, window):
     assert (pf.double() - ref).abs().max() < 1e-4 and (dc.double() - ref).abs().max() < 1e-4
 
 
-def test_pair_embedding_carries_the_last_token_of_a_slot(lib):
+@pytest.mark.parametrize('W', [40, 44, 2048])                  # 16-byte path, scalar path, rows longer than one pass of the CTA
+def test_pair_embedding_carries_the_last_token_of_a_slot(lib, W):
     from phi3_b200._lib import call, ptr
     dev = torch.device('cuda')
-    W, V, buckets, mp, mc, n_slots = 40, 50, 13, 1000003, 7, 3
+    V, buckets, mp, mc, n_slots = 50, 13, 1000003, 7, 3
     g = torch.Generator().manual_seed(5)
     table, pairs = torch.randn(V, W, generator=g).bfloat16(), torch.randn(buckets + 1, W, generator=g).bfloat16()
     hist = {1: torch.randint(0, V, (9,), generator=g).tolist(), 2: torch.randint(0, V, (4,), generator=g).tolist()}
