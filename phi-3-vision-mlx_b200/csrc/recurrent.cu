@@ -493,9 +493,10 @@ extern "C" int p3_gla_scan(const p3_gla_args* a, cudaStream_t st) {
         const unsigned blocks = (unsigned)(work + 255) / 256 < 148u * 8 ? (unsigned)((work + 255) / 256) : 148u * 8;
         p3_launch_pdl(gla_decay_kernel, dim3(blocks ? blocks : 1), dim3(256), (size_t)(0), st, a->z, a->ld_z, a->z_bias, (int64_t)a->n_rows, n, a->inv_tau, vec);
     }
-    // the shape of a warp as for the matrix memory: four row slices x eight lanes, two columns per lane when that still leaves a
-    // CTA for every SM
-    int rs = 4, nc = (int64_t)a->n_seqs * a->n_heads * ((a->vdim + 63) / 64) >= 148 ? 2 : 1;
+    // A warp is four row slices x eight lanes. Two columns per lane halve the shared-memory reads per FMA, which is what bounds
+    // this kernel (three staged rows per token against two of the matrix memory): a CTA then takes 1.14 times as long for twice
+    // the columns, so that shape wins as soon as one column per lane would need more CTAs than there are SMs.
+    int rs = 4, nc = (int64_t)a->n_seqs * a->n_heads * ((a->vdim + 31) / 32) > 148 ? 2 : 1;
     if (a->rs_force == 2 || a->rs_force == 4) { rs = a->rs_force; nc = 1; }
     if (a->rs_force == 8) { rs = 4; nc = 2; }
     if (a->dim > 256) { rs = 4; nc = 1; }                    // 128 rows per thread, 16 tokens per round
