@@ -430,17 +430,32 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
     const float fpos = (float)pos;
     // where the two numbers of rotation pair i live in a turning part
     const int pa = a.pair_mode ? 2 : 1, pb = a.pair_mode ? 1 : half;
-    for (int job = blockIdx.y * nw + warp; job < 2 + H; job += gridDim.y * nw) {
-        if (job == 1 + H) {                                  // the query's low-rank vector: RMS norm -> input of the query up-projection
-            if (a.q_rank <= 0) continue;
-            const float* c = pr + a.cq_off;
-            AT* dst = (AT*)a.cq_out + (size_t)t * a.ld_cq;
-            float ss = 0.f;
-            for (int i = lane; i < a.q_rank; i += 32) ss = fmaf(c[i], c[i], ss);
-            ss = warp_sum(ss);
-            const float rs = 1.0f / sqrtf(ss / (float)a.q_rank + a.eps);
-            for (int i = lane; i < a.q_rank; i += 32) stv(dst + i, c[i] * rs * a.cq_gain[i]);
-        } else if (job == 0) {
+    if (a.q_rank > 0 && blockIdx.y == 0) {
+        // the query's low-rank vector: RMS norm -> input of the query up-projection. It is the longest row of the kernel, so the
+        // whole CTA shares it (up to RPT numbers per thread stay in registers between the statistic and the write)
+        __shared__ float sh[32];
+        const float* c = pr + a.cq_off;
+        AT* dst = (AT*)a.cq_out + (size_t)t * a.ld_cq;
+        const int nt = blockDim.x;
+        float v[RPT], gv[RPT];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            const int i = threadIdx.x + k * nt;
+            v[k] = i < a.q_rank ? c[i] : 0.f;
+            gv[k] = i < a.q_rank ? a.cq_gain[i] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < RPT; k++) ss = fmaf(v[k], v[k], ss);
+        for (int i = threadIdx.x + RPT * nt; i < a.q_rank; i += nt) ss = fmaf(c[i], c[i], ss);
+        ss = block_sum(ss, sh);
+        const float rs = 1.0f / sqrtf(ss / (float)a.q_rank + a.eps);
+#pragma unroll
+        for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; if (i < a.q_rank) stv(dst + i, v[k] * rs * gv[k]); }
+        for (int i = threadIdx.x + RPT * nt; i < a.q_rank; i += nt) stv(dst + i, c[i] * rs * a.cq_gain[i]);
+    }
+    for (int job = blockIdx.y * nw + warp; job < 1 + H; job += gridDim.y * nw) {
+        if (job == 0) {
             if (!a.cache) continue;
             const float* c = pr + a.c_off;
             CT* dst = (CT*)a.cache + ((size_t)page * P3_PAGE + off) * (R + dr);
@@ -1051,7 +1066,7 @@ extern "C" int p3_latent_post(const p3_latent_post_args* a, cudaStream_t st) {
     P3_CHECK_ARG(a->rot_n >= 0 && a->rot_n <= a->rot_dim && a->rot_n % 2 == 0, "latent_post: rot_n must be even and <= rot_dim");
     P3_CHECK_ARG(a->n_ff == 0 || a->hid, "latent_post: the gated unit needs its output");
     if (a->T == 0) return 0;
-    const int jobs = 2 + a->n_heads, th = 128;
+    const int jobs = 1 + a->n_heads, th = 128;
     // few tokens: one warp per job and enough CTAs for the gated unit's columns; many tokens: one CTA per token
     int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
     if (a->T < 1024 && groups < (a->n_ff + 2047) / 2048) groups = (a->n_ff + 2047) / 2048;

@@ -633,7 +633,7 @@ def test_pair_embedding_carries_the_last_token_of_a_slot(lib, W):
 
 
 @pytest.mark.parametrize('dtype', [F32, B16])
-@pytest.mark.parametrize('sizes', [(3, 16, 8, 24, 40, 8), (2, 7, 6, 5, 11, 2), (4, 32, 32, 32, 64, 32)])
+@pytest.mark.parametrize('sizes', [(3, 16, 8, 24, 40, 8), (2, 7, 6, 5, 11, 2), (4, 32, 32, 32, 64, 32), (2, 8, 4, 1100, 16, 4)])
 def test_latent_post_norms_neighbour_pairs_and_both_calls(lib, dtype, sizes):
     """the two calls of the latent post kernel against plain torch: low-rank query vector and latent vector normed, the shared key
     part rotated as neighbour pairs into the cache row; then the query parts from a second product split and rotated"""
