@@ -14,7 +14,7 @@ row ends. This engine serves a stream of requests instead:
                               p3_row_stats / p3_top_p_sample kernels, and frees a request's pages the step it finishes.
 
 A model plugs in with kv_layout(), cache_dtype(), prepare(max_context) and forward(StepBatch, pool) (tagenex.TagenexB200), and
-with state_layout() when its layers carry a recurrent state per sequence (dugalix.DugalixB200): the pool then keeps one row of
+with state_layout() when its layers carry a recurrent state per sequence (dugalix.DugalixB200, danalorn.DanalornB200): the pool then keeps one row of
 fp32 numbers per slot and state buffer, and the step's descriptors list the sequences of the step (first row, rows, slot, first
 position) for the kernels that walk a sequence's rows in order.
 """

@@ -1,6 +1,6 @@
 """What the engine models (decoders with an fp32 residual stream that run a ragged token batch against the shared page pool) have in
 common: the description of a step, the choice of the matrix-product kernel, the grouped expert products and the key-slice cost model
-of the decode attention. A design (tagenex.py, tapalix.py) owns its weights and the order of its kernels; it has no cache and no loop
+of the decode attention. A design (tagenex.py, tapalix.py, dugalix.py, danalorn.py) owns its weights and the order of its kernels; it has no cache and no loop
 of its own.
 
 Matrix products. Dense bf16 products with K % 8 == 0 run on the tcgen05 GEMM (p3_gemm); batches of at most 16 tokens on the

@@ -6,11 +6,11 @@ allocated once, a sequence takes a slot (one row of the block table) when it is 
 tokens arrive, and gives both back when it ends, so pages and slots are used again by later requests.
 
 Per layer there is one K pool [page][kv heads][64][key size] and one V pool [page][kv heads][64][value size]; the sizes may
-differ between layers (`layout` = [(kv_heads, key size, value size), ...]). Pools are zero-initialised and only ever hold finite
+differ between layers (`layout` = [(kv_heads, key size, value size), ...]; a layer without a cache of its own gives zeros). Pools are zero-initialised and only ever hold finite
 numbers, so a masked slot can never poison a weighted sum. The block table lives on the device; the host keeps a mirror and
 uploads the rows that changed before a step.
 
-Recurrent state. A model whose layers carry a state from token to token (a token shift, a matrix memory) names the fp32 numbers
+Recurrent state. A model whose layers carry a state from token to token (a token shift, a matrix memory, the last token) names the fp32 numbers
 each of its state buffers needs per sequence (`state_layout` = [numbers per slot, ...]); the pool allocates them once as
 [slots][numbers] and a sequence's state lives in the row of its slot. Nothing is cleared when a slot changes hands: the kernels
 start a sequence whose first token has position 0 from the zero state whatever the row holds.
