@@ -765,13 +765,13 @@ def run_dugalix(args):
 def _danalorn_cfg(width, heads, kv, dim, lat_dim, lat_rot, rank, q_rank, window, gh, gdim, gvdim, ff, layers, vocab):
     lat = {'type': 'latent_attention',
            'mixer': {'heads': heads, 'dim': lat_dim, 'rot_dim': lat_rot, 'vdim': lat_dim, 'kv_rank': rank, 'q_rank': q_rank,
-                     'scale': (lat_dim + lat_rot) ** -0.5, 'mask': {'size': window}, 'rot': {'base': 500000.0, 'dims': lat_rot}}}
+                     'scale': (lat_dim + lat_rot) ** -0.5, 'mask': {'size': window}, 'rot': {'base': 10000.0, 'dims': lat_rot}}}
     att = {'type': 'attention', 'mixer': {'heads': heads, 'kv_heads': kv, 'dim': dim, 'vdim': dim, 'scale': dim ** -0.5,
-                                          'q_temp': {'coef': 0.3, 'every': 64}}}
-    gla = {'type': 'gla', 'mixer': {'heads': gh, 'dim': gdim, 'vdim': gvdim, 'tau': 16.0}}
+                                          'q_temp': {'coef': 0.25, 'every': 128}}}
+    gla = {'type': 'gla', 'mixer': {'heads': gh, 'dim': gdim, 'vdim': gvdim, 'tau': 8.0}}
     order = [lat, att, gla, gla]
     return {'architecture': 'Danalorn', 'vocab': vocab, 'width': width, 'norm': {'eps': 1e-5},
-            'embedding': {'scale': width ** 0.5, 'bigram': {'buckets': 65521, 'mul_prev': 31, 'mul_cur': 7}},
+            'embedding': {'scale': width ** 0.5, 'bigram': {'buckets': 65521, 'mul_prev': 37, 'mul_cur': 11}},
             'layers': [dict(order[i % 4], mlp={'kind': 'dense', 'ff': ff}) for i in range(layers)]}
 
 

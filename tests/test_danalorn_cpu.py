@@ -84,10 +84,10 @@ def test_page_pool_allocates_nothing_for_layers_without_a_cache():
 def test_oracle_pair_embedding_rows():
     W = 4
     w = {'embed': torch.arange(10 * W, dtype=F64).view(10, W), 'bigram': 100.0 * torch.arange(8, dtype=F64)[:, None].repeat(1, W)}
-    ec = {'scale': 2.0, 'bigram': {'buckets': 7, 'mul_prev': 31, 'mul_cur': 5}}
+    ec = {'scale': 2.0, 'bigram': {'buckets': 7, 'mul_prev': 37, 'mul_cur': 5}}
     toks = [3, 9, 9, 0]
     x = O.embed(toks, w, ec, F64)
-    rows = [7, (3 * 31 + 9 * 5) % 7, (9 * 31 + 9 * 5) % 7, (9 * 31 + 0) % 7]       # the first token takes the table's last row
+    rows = [7, (3 * 37 + 9 * 5) % 7, (9 * 37 + 9 * 5) % 7, (9 * 37 + 0) % 7]       # the first token takes the table's last row
     for t, (tok, r) in enumerate(zip(toks, rows)):
         assert torch.equal(x[t], w['embed'][tok] * 2.0 + 100.0 * r)
     assert torch.equal(O.embed(toks, w, {'scale': 0.5}, F64), w['embed'][torch.tensor(toks)] * 0.5)
@@ -159,7 +159,7 @@ def test_oracle_latent_attention_equals_explicit_keys_and_values():
 def test_oracle_biased_attention_temperature_distance_bias_and_gate():
     torch.manual_seed(1)
     T, W, H, G, d, dv = 9, 8, 4, 2, 3, 5
-    mc = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=0.5, q_temp={'coef': 0.3, 'every': 4})
+    mc = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=0.5, q_temp={'coef': 0.45, 'every': 4})
     w = {'p.' + n: torch.randn(s, dtype=F64) for n, s in dict(q=(H * d, W), k=(G * d, W), v=(G * dv, W), g=(H * dv, W), o=(W, H * dv)).items()}
     for n, s in (('q.b', H * d), ('k.b', G * d), ('v.b', G * dv)):
         w['p.' + n] = torch.randn(s, dtype=F64)
@@ -173,7 +173,7 @@ def test_oracle_biased_attention_temperature_distance_bias_and_gate():
     heads = torch.zeros(T, H, dv, dtype=F64)
     for hh in range(H):
         for t in range(T):
-            temp = 1 + 0.3 * math.log((t + 1) // 4 + 1)        # grows at positions 3, 7, ...: (t + 1) counted in steps of 4
+            temp = 1 + 0.45 * math.log((t + 1) // 4 + 1)        # grows at positions 3, 7, ...: (t + 1) counted in steps of 4
             sc = torch.stack([(q[t, hh] * temp) @ k[j, hh // 2] * 0.5 - 2.0 ** (-8 * (hh + 1) / H) * (t - j) for j in range(t + 1)])
             e = torch.exp(sc)
             heads[t, hh] = ((e / (1 + e.sum()))[:, None] * v[:t + 1, hh // 2]).sum(0)

@@ -314,10 +314,10 @@ OTHER = {
              [dict(_la(1, 16, 16, 16, 16, 16, 1), mlp=_dense(64)), dict(_att(1, 1, 16, 16, (1.0, 1)), mlp=_dense(64)),
               dict(_gla(1, 16, 16, 1.0, 1), mlp=None), dict(_la(1, 8, 16, 8, 16, 8, 2, kv_from=0), mlp=_dense(16))]),
     # sizes that tile the tensor-core kernels and equal each other; the borrowing layer comes right after its source
-    'tiled': (128, dict(bigram=(1021, 31, 7), embed_scale=11.3),
+    'tiled': (128, dict(bigram=(1031, 37, 11), embed_scale=11.3),
               [dict(_la(4, 32, 32, 32, 96, 64, 64), mlp=_dense(256)), dict(_la(8, 32, 32, 64, 96, 128, 65, kv_from=0), mlp=_dense(128)),
-               dict(_att(8, 2, 64, 64, (0.3, 64)), mlp=_dense(256)), dict(_gla(4, 64, 64, 16.0), mlp=_dense(256)),
-               dict(_att(4, 4, 128, 128), mlp=_dense(128)), dict(_gla(2, 128, 128, 16.0, 32), mlp=_dense(128))]),
+               dict(_att(8, 2, 64, 64, (0.25, 32)), mlp=_dense(256)), dict(_gla(4, 64, 64, 12.0), mlp=_dense(256)),
+               dict(_att(4, 4, 128, 128), mlp=_dense(128)), dict(_gla(2, 128, 128, 20.0, 32), mlp=_dense(128))]),
     # nothing is a multiple of 8: every product goes through the any-shape kernel, every attention through the fp32 kernels
     'ragged': (50, dict(bigram=(97, 1000003, 999983), embed_scale=0.5),
                [dict(_gla(3, 7, 9, 2.5, 3), mlp=_dense(33)), dict(_la(3, 10, 6, 7, 11, 13, 63, rdims=2), mlp=_dense(21)),
@@ -375,14 +375,14 @@ def _random_config(rng):
             else:
                 rd = rng.choice([2, 8, 16])
                 lay = _la(heads, dim, rd, vdim, rng.choice([16, 24, 56]), rng.choice([8, 24, 40]), win,
-                          rdims=rng.choice([d for d in (2, 4, 8, 16) if d <= rd]), base=rng.choice([100.0, 10000.0, 500000.0]))
+                          rdims=rng.choice([d for d in (2, 4, 8, 16) if d <= rd]), base=rng.choice([100.0, 10000.0, 1000000.0]))
                 sources.append(i)
         elif kind == 'attention':
             kv = rng.randint(1, 3)
             lay = _att(kv * rng.randint(1, 3), kv, rng.choice([8, 16, 40]), rng.choice([8, 24, 32]),
-                       rng.choice([None, (0.3, 64), (0.7, 5), (0.1, 1)]))
+                       rng.choice([None, (0.25, 32), (0.7, 5), (0.1, 1)]))
         else:
-            lay = _gla(rng.randint(1, 4), rng.choice([8, 24, 40, 72]), rng.choice([8, 24, 40, 70]), rng.choice([1.0, 4.0, 16.0]),
+            lay = _gla(rng.randint(1, 4), rng.choice([8, 24, 40, 72]), rng.choice([8, 24, 40, 70]), rng.choice([1.0, 4.0, 12.0]),
                        rng.choice([2, 8, 16]))
         layers.append(dict(lay, mlp=mlp))
     bigram = rng.choice([None, (rng.choice([5, 64, 509]), rng.randint(1, 99), rng.randint(1, 99))])
@@ -722,7 +722,7 @@ def test_query_key_norm_with_biases_and_query_temperature(lib, dtype):
 
 
 @pytest.mark.parametrize('shape', [(2, 24, 40), (1, 7, 5), (3, 64, 64), (2, 128, 96), (1, 200, 33), (5, 136, 70), (1, 300, 40)])
-@pytest.mark.parametrize('tau,rs', [(16.0, 0), (1.0, 0), (4.0, 2), (4.0, 4), (4.0, 8)])
+@pytest.mark.parametrize('tau,rs', [(12.0, 0), (1.0, 0), (4.0, 2), (4.0, 4), (4.0, 8)])
 def test_gla_scan_in_portions_and_with_decays_at_both_ends(lib, shape, tau, rs):
     """the recurrence alone: whole sequences against the token loop of the oracle, then the same sequences in portions (the state
     rows carry on) with a second sequence in the batch, bit for bit equal to the whole run. Decay logits reach far to both sides:
