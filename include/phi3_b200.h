@@ -567,8 +567,11 @@ int p3_distance_linear_table(const float* slope, float* pen, int H, int n, cudaS
  * token by token over the rows of every sequence of `seqs`. q at q_off, k at k_off (heads x dim) and v at v_off (heads x vdim) are
  * columns of proj (fp32 [T, ld_proj]); the decay logits z fp32 [n_rows, ld_z] (heads x dim, z_bias fp32 [heads * dim] or NULL) come
  * from a product of their own and are REPLACED by the decays (a first launch over all n_rows rows of the step; the sequences of
- * `seqs` lie inside them). out fp32 [T, ld_out], head h at column h * vdim. The state of a slot is `state + slot *
- * p3_gla_state_floats(...)` floats, read at the start and written at the end of the step. rs_force as for the matrix memory. */
+ * `seqs` lie inside them). With lr (fp32 [n_rows, ld_lr], `rank` <= 64 numbers per row: the low-rank vector of the decay projection,
+ * e.g. columns of proj) and a2 (fp32 [heads * dim][rank]) that first launch forms the logits itself, z = a2 lr (+ z_bias, fp32 FMA
+ * chain in ascending rank index), and z is only written. out fp32 [T, ld_out], head h at column h * vdim. The state of a slot is
+ * `state + slot * p3_gla_state_floats(...)` floats, read at the start and written at the end of the step. rs_force as for the
+ * matrix memory. */
 typedef struct {
     const float* proj; int64_t ld_proj; int32_t q_off, k_off, v_off;
     float* z; int64_t ld_z; const float* z_bias; float inv_tau;
@@ -576,6 +579,7 @@ typedef struct {
     float* state; const int32_t* seqs; int32_t n_seqs;
     float* out; int64_t ld_out; int32_t rs_force;
     int32_t n_rows;
+    const float* lr; int64_t ld_lr; const float* a2; int32_t rank;
 } p3_gla_args;
 int64_t p3_gla_state_floats(int n_heads, int dim, int vdim);
 int p3_gla_scan(const p3_gla_args* args, cudaStream_t st);

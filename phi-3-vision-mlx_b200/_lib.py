@@ -280,4 +280,4 @@ class GlaArgs(C.Structure):
                 ('z', _p), ('ld_z', _l), ('z_bias', _p), ('inv_tau', C.c_float),
                 ('n_heads', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('q_scale', C.c_float),
                 ('state', _p), ('seqs', _p), ('n_seqs', C.c_int32), ('out', _p), ('ld_out', _l), ('rs_force', C.c_int32),
-                ('n_rows', C.c_int32)]
+                ('n_rows', C.c_int32), ('lr', _p), ('ld_lr', _l), ('a2', _p), ('rank', C.c_int32)]

@@ -268,6 +268,42 @@ __global__ void gla_decay_kernel(float* __restrict__ z, int64_t ld_z, const floa
     }
 }
 
+// the same with the logits formed on the way: z[t][c] = exp(logsigmoid(bias[c] + sum_r lr[t][r] a2[c][r]) * inv_tau). A thread owns
+// one column with its a2 row in registers and walks the tokens of its CTA's chunk, whose low-rank vectors are staged in shared
+// memory 32 tokens at a time (every thread reads the same number: a broadcast); the FMA chain runs in ascending r.
+constexpr int GD_TOK = 32;
+template <int RMAX>
+__global__ void __launch_bounds__(256) gla_decay_lowrank_kernel(float* __restrict__ z, int64_t ld_z, const float* __restrict__ bias,
+                                                                const float* __restrict__ lr, int64_t ld_lr, const float* __restrict__ a2,
+                                                                int rank, int64_t T, int n, float inv_tau, int tok_per_cta) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    __shared__ float lrs[GD_TOK][RMAX];
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    float w[RMAX];
+#pragma unroll
+    for (int r = 0; r < RMAX; r++) w[r] = (c < n && r < rank) ? a2[(size_t)c * rank + r] : 0.f;
+    const float b = (c < n && bias) ? bias[c] : 0.f;
+    const int64_t t_end = min(T, (int64_t)(blockIdx.y + 1) * tok_per_cta);
+    for (int64_t t0 = (int64_t)blockIdx.y * tok_per_cta; t0 < t_end; t0 += GD_TOK) {
+        const int nb = (int)min((int64_t)GD_TOK, t_end - t0);
+        __syncthreads();                                     // the round before is consumed
+        for (int i = threadIdx.x; i < nb * RMAX; i += 256) {
+            const int tt = i / RMAX, r = i - tt * RMAX;
+            lrs[tt][r] = r < rank ? lr[(t0 + tt) * ld_lr + r] : 0.f;
+        }
+        __syncthreads();
+        if (c < n) {
+            for (int tt = 0; tt < nb; tt++) {
+                float acc = b;
+#pragma unroll
+                for (int r = 0; r < RMAX; r++) acc = fmaf(lrs[tt][r], w[r], acc);
+                z[(t0 + tt) * ld_z + c] = expf(log_sigmoid(acc) * inv_tau);
+            }
+        }
+    }
+}
+
 constexpr int GLA_WARPS = 4;     // every warp owns columns of S
 
 template <int DS, int RS, int NC, int TB>
@@ -486,7 +522,20 @@ extern "C" int p3_gla_scan(const p3_gla_args* a, cudaStream_t st) {
     P3_CHECK_ARG(((uintptr_t)a->seqs & 15) == 0, "gla_scan: the sequence records must be 16-byte aligned");
     P3_CHECK_ARG(a->n_rows >= 0, "gla_scan: the number of rows must not be negative");
     if (a->n_seqs == 0 || a->n_rows == 0) return 0;
-    {   // decays first, over all rows of the step at once and in place: the scan then stages them like k and q
+    P3_CHECK_ARG(!a->lr || (a->a2 && a->rank >= 1 && a->rank <= 64), "gla_scan: the low-rank decay projection needs a2 and 1 <= rank <= 64");
+    if (a->lr) {   // decays first, over all rows of the step at once, logits formed on the way: the scan then stages them like k and q
+        const int n = a->n_heads * a->dim;
+        const unsigned gx = (unsigned)((n + 255) / 256);
+        // enough CTAs for four per SM, at least one staged round of tokens each
+        int64_t per = (a->n_rows + (148 * 4 / gx)) / (148 * 4 / gx + 1);
+        per = (per + GD_TOK - 1) / GD_TOK * GD_TOK;
+        if (per < GD_TOK) per = GD_TOK;
+        const dim3 dgrid(gx, (unsigned)((a->n_rows + per - 1) / per));
+#define GD(R) p3_launch_pdl(gla_decay_lowrank_kernel<R>, dim3(dgrid), dim3(256), (size_t)(0), st, a->z, a->ld_z, a->z_bias, a->lr, a->ld_lr, \
+                            a->a2, a->rank, (int64_t)a->n_rows, n, a->inv_tau, (int)per)
+        if (a->rank <= 16) GD(16); else if (a->rank <= 32) GD(32); else GD(64);
+#undef GD
+    } else {       // decays first, over all rows of the step at once and in place
         const int n = a->n_heads * a->dim;
         const int vec = n % 4 == 0 && a->ld_z % 4 == 0 && ((uintptr_t)a->z & 15) == 0 && (!a->z_bias || ((uintptr_t)a->z_bias & 15) == 0);
         const int64_t work = (int64_t)a->n_rows * (vec ? n / 4 : n);

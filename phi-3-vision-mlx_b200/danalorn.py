@@ -27,7 +27,7 @@ Kernels per layer (csrc/): p3_embed_pair_rows_f32 -> p3_postnorm_prenorm ->
              _decode (window, sink) -> per-head value up-projection -> output product
   attention: ONE product [q | k | v | gate] -> p3_qkv_post (biases, head norms, query temperature, paged K/V write) ->
              p3_attn_window_prefill / _decode (distance table, unit sink, element-wise gate in the epilogue) -> output product
-  gla:       ONE product [q | k | v | gate] + decay down product -> decay up product -> p3_gla_scan (decays in place, then the
+  gla:       ONE product [q | k | v | gate | decay down] -> p3_gla_scan (decay up-projection, bias and decays in one pass, then the
              scan) -> p3_headnorm_gate_x -> output product
 -> p3_postnorm_prenorm -> up product -> p3_relu2 -> down product -> p3_postnorm_prenorm.
 
@@ -36,6 +36,7 @@ positions, angles, scores, softmax, norms, the residual sum, decays and their lo
 dtype=float32: everything is fp32 on the FMA pipes (no TF32).
 """
 import ctypes as C
+import os
 
 import torch
 from . import _lib
@@ -129,9 +130,15 @@ class DanalornB200(PagedLM):
                 expect(a + 'o', (W, H * dv)); expect(a + 'norm', (dv,)); expect(a + 'a2.b', (H * d,))
                 r = w[a + 'a1'].shape[0]                                       # rank of the decay projection: the tensors give it
                 expect(a + 'a1', (r, W)); expect(a + 'a2', (H * d, r))
-                L['in_w'] = rows16([w[a + 'q'], w[a + 'k'], w[a + 'v'], w[a + 'g']])
-                L['a1'], L['a2'], L['a2_b'] = mat(w[a + 'a1']), mat(w[a + 'a2']), f32(w[a + 'a2.b'])
-                L['gain'], L['out_w'] = f32(w[a + 'norm']), mat(w[a + 'o'])
+                # decay ranks up to 64: the down projection's rows ride in the layer's input product and the scan's first launch forms
+                # the logits from them (fp32); above that the two decay projections are products of their own
+                L['rank'], L['fused_decay'] = r, r <= 64 and os.environ.get('P3_GLA_FUSED_DECAY', '1') != '0'
+                L['in_w'] = rows16([w[a + 'q'], w[a + 'k'], w[a + 'v'], w[a + 'g']] + ([w[a + 'a1']] if L['fused_decay'] else []))
+                if L['fused_decay']:
+                    L['a2_32'] = f32(w[a + 'a2'])
+                else:
+                    L['a1'], L['a2'] = mat(w[a + 'a1']), mat(w[a + 'a2'])
+                L['a2_b'], L['gain'], L['out_w'] = f32(w[a + 'a2.b']), f32(w[a + 'norm']), mat(w[a + 'o'])
                 L['state'] = len(self._state_layout)
                 self._state_layout.append(int(_lib.lib().p3_gla_state_floats(H, d, dv)))
                 L['tile_rows'] = 64
@@ -346,12 +353,16 @@ class DanalornB200(PagedLM):
         H, d, dv = m.heads, m.dim, m.vdim
         proj = e(T, L['in_w'].shape[0])
         self.linear(h, L['in_w'], proj, nxt=L['out_w'])
-        # decay logits through their low-rank projection (the bias joins in the scan)
-        lr, z = e(T, L['a1'].shape[0], dt=act), e(T, H * d)
-        self.linear(h, L['a1'], lr)
-        self.linear(lr, L['a2'], z)
+        z = e(T, H * d)                                       # decay logits, then decays
         y = e(T, H * dv)
         r = _lib.GlaArgs()
+        if L['fused_decay']:
+            lr = proj[:, 2 * H * d + 2 * H * dv:]
+            r.lr, r.ld_lr, r.a2, r.rank = ptr(lr), proj.stride(0), ptr(L['a2_32']), L['rank']
+        else:
+            lr = e(T, L['rank'], dt=act)
+            self.linear(h, L['a1'], lr)
+            self.linear(lr, L['a2'], z)
         r.proj, r.ld_proj, r.q_off, r.k_off, r.v_off = ptr(proj), proj.stride(0), 0, H * d, 2 * H * d
         r.z, r.ld_z, r.z_bias, r.inv_tau = ptr(z), z.stride(0), ptr(L['a2_b']), 1.0 / m.tau
         r.n_heads, r.dim, r.vdim, r.q_scale = H, d, dv, d ** -0.5

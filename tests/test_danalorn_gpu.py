@@ -318,16 +318,18 @@ OTHER = {
               [dict(_la(4, 32, 32, 32, 96, 64, 64), mlp=_dense(256)), dict(_la(8, 32, 32, 64, 96, 128, 65, kv_from=0), mlp=_dense(128)),
                dict(_att(8, 2, 64, 64, (0.25, 32)), mlp=_dense(256)), dict(_gla(4, 64, 64, 12.0), mlp=_dense(256)),
                dict(_att(4, 4, 128, 128), mlp=_dense(128)), dict(_gla(2, 128, 128, 20.0, 32), mlp=_dense(128))]),
-    # nothing is a multiple of 8: every product goes through the any-shape kernel, every attention through the fp32 kernels
+    # nothing is a multiple of 8: every product goes through the any-shape kernel, every attention through the fp32 kernels; the last
+    # layer has no turning part at all
     'ragged': (50, dict(bigram=(97, 1000003, 999983), embed_scale=0.5),
                [dict(_gla(3, 7, 9, 2.5, 3), mlp=_dense(33)), dict(_la(3, 10, 6, 7, 11, 13, 63, rdims=2), mlp=_dense(21)),
                 dict(_att(6, 2, 10, 14, (2.0, 3)), mlp=None), dict(_la(2, 5, 6, 9, 11, 9, 0, rdims=2, kv_from=1), mlp=_dense(19)),
-                dict(_gla(1, 130, 5, 30.0, 5), mlp=_dense(10))]),
-    # no pair table, two sources with two borrowers each way around, a window longer than anything fed, wide heads
+                dict(_gla(1, 130, 5, 30.0, 5), mlp=_dense(10)), dict(_la(2, 12, 0, 10, 20, 6, 9), mlp=_dense(12))]),
+    # no pair table, two sources with two borrowers each way around, a window longer than anything fed, wide heads, a decay
+    # projection of rank 80 (products of its own) and one of rank 33
     'wide': (96, dict(bigram=None, embed_scale=3.0),
              [dict(_la(2, 64, 64, 96, 128, 48, 1000), mlp=_dense(96)), dict(_la(3, 24, 16, 40, 56, 24, 40), mlp=None),
               dict(_la(2, 16, 16, 24, 56, 40, 20, kv_from=1), mlp=_dense(48)), dict(_la(4, 32, 64, 32, 128, 96, 33, kv_from=0), mlp=None),
-              dict(_att(12, 1, 24, 200), mlp=_dense(48)), dict(_gla(2, 260, 72, 9.0), mlp=_dense(40))]),
+              dict(_att(12, 1, 24, 200), mlp=_dense(48)), dict(_gla(2, 260, 72, 9.0, 80), mlp=_dense(40)), dict(_gla(2, 16, 24, 5.0, 33), mlp=None)]),
 }
 
 
@@ -721,7 +723,7 @@ def test_query_key_norm_with_biases_and_query_temperature(lib, dtype):
         assert (kp[pg, :, off].float().cpu() - k_ref[t]).abs().max() < tol and (vp[pg, :, off].float().cpu() - v_ref[t]).abs().max() < tol
 
 
-@pytest.mark.parametrize('shape', [(2, 24, 40), (1, 7, 5), (3, 64, 64), (2, 128, 96), (1, 200, 33), (5, 136, 70), (1, 300, 40)])
+@pytest.mark.parametrize('shape', [(2, 24, 40), (1, 7, 5), (3, 20, 64), (3, 64, 64), (2, 128, 96), (1, 200, 33), (5, 136, 70), (1, 300, 40)])
 @pytest.mark.parametrize('tau,rs', [(12.0, 0), (1.0, 0), (4.0, 2), (4.0, 4), (4.0, 8)])
 def test_gla_scan_in_portions_and_with_decays_at_both_ends(lib, shape, tau, rs):
     """the recurrence alone: whole sequences against the token loop of the oracle, then the same sequences in portions (the state
@@ -784,6 +786,30 @@ def test_gla_scan_in_portions_and_with_decays_at_both_ends(lib, shape, tau, rs):
         return {s: torch.cat(v, 0) for s, v in got.items()}
 
     whole = run([[(1, 0, 83), (2, 0, 37)]])                    # sequence s lives in slot s + 1
+    if rs == 0:
+        # the same logits as a low-rank product formed by the scan's first launch: z = a2 lr, with a2 = [I | 0] and lr = [z | junk]
+        if H * d <= 64:
+            lr_all = {s_: torch.cat([z[s_], torch.randn(T[s_], 3, generator=g)], 1) for s_ in T}
+            a2m = torch.cat([torch.eye(H * d), torch.zeros(H * d, 3)], 1)
+            state = torch.full((3, n_state), float('nan'), device=dev)
+            for s_ in T:
+                n = T[s_]
+                pd, ld_, a2d = proj[s_].to(dev), lr_all[s_].to(dev), a2m.to(dev)
+                zd = torch.full((n, H * d), float('nan'), device=dev)
+                y, out = torch.empty(n, H * dv, device=dev), torch.empty(n, H * dv, device=dev)
+                sq = torch.tensor([(0, n, s_ + 1, 0)], dtype=torch.int32, device=dev).reshape(-1)
+                zbd, gd = zb.to(dev), gain.to(dev)
+                a = GlaArgs()
+                a.proj, a.ld_proj, a.q_off, a.k_off, a.v_off = ptr(pd), cols, off['q'], off['k'], off['v']
+                a.z, a.ld_z, a.z_bias, a.inv_tau = ptr(zd), H * d, ptr(zbd), 1.0 / tau
+                a.lr, a.ld_lr, a.a2, a.rank = ptr(ld_), ld_.shape[1], ptr(a2d), a2m.shape[1]
+                a.n_heads, a.dim, a.vdim, a.q_scale = H, d, dv, d ** -0.5
+                a.state, a.seqs, a.n_seqs, a.out, a.ld_out, a.n_rows = ptr(state), ptr(sq), 1, ptr(y), H * dv, n
+                call_struct('p3_gla_scan', a, 0)
+                call('p3_headnorm_gate_x', ptr(y), H * dv, None, H, dv, ptr(gd), 1, ptr(pd[:, off['g']:]), cols, 1, 1.0, 1e-6, ptr(out),
+                     H * dv, 1, n, 0)
+                torch.cuda.synchronize()
+                assert (out.cpu().double() - ref[s_]).abs().max() < 2e-4 * max(1.0, float(ref[s_].abs().max())), s_
     parts = run([[(1, 0, 17)], [(2, 0, 2), (1, 17, 1)], [(1, 18, 16), (2, 2, 33)], [(1, 34, 1)], [(2, 35, 2), (1, 35, 48)]])
     for s in T:
         scale = float(ref[s].abs().max())
