@@ -470,10 +470,11 @@ class DanalornConfig:
         return [2.0 ** (-self.SLOPE_OCTAVES * (h + 1) / heads) for h in range(heads)]
 
 
-def tiny_danalorn(width=96, vocab=300, layers=None, eps=1e-5, bigram=(257, 29, 5), embed_scale=7.0):
+def tiny_danalorn(width=96, vocab=300, layers=None, eps=1e-5, bigram=(257, 29, 5), embed_scale=1.5):
     """A small Danalorn config dict for tests: sizes deliberately unequal between layers (dim != vdim != rot_dim, heads != kv_heads,
     partly rotated turning parts, windows that differ), a latent layer that reads an earlier layer's cache, one layer without a
-    feed-forward, an attention layer without a query temperature."""
+    feed-forward, an attention layer without a query temperature. The embedding's scale is small, so that the layers' outputs and
+    not the first rows of the residual stream decide the logits."""
     la = lambda heads, dim, rd, vdim, rank, qrank, win, rdims=None, base=10000.0, kv_from=None: {
         'type': 'latent_attention',
         'mixer': dict(heads=heads, dim=dim, rot_dim=rd, vdim=vdim, kv_rank=rank, q_rank=qrank, scale=(dim + rd) ** -0.5,

@@ -16,7 +16,7 @@ F64 = torch.float64
 def test_config_reads_every_size_and_constant():
     d = configs.tiny_danalorn()
     c = configs.DanalornConfig(d)
-    assert c.vocab_size == 300 and c.width == 96 and c.eps == 1e-5 and c.embed_scale == 7.0 and len(c.layers) == 7
+    assert c.vocab_size == 300 and c.width == 96 and c.eps == 1e-5 and c.embed_scale == 1.5 and len(c.layers) == 7
     assert (c.bigram.buckets, c.bigram.mul_prev, c.bigram.mul_cur) == (257, 29, 5)
     assert [l.mixer.kind for l in c.layers] == ['gla', 'latent_attention', 'attention', 'latent_attention', 'attention',
                                                 'latent_attention', 'gla']
