@@ -1,6 +1,7 @@
 // Paged attention over a ragged batch with a sliding window, a per-head sink in the softmax denominator and a per-head distance
 // penalty: score(i, j) = scale * q_i . k_j - pen[h][i - j], visible when 0 <= i - j < window (window 0: every earlier key),
-// weights = exp(score) / (exp(sink_h) + sum over visible exp(score)); optional per-(token, head) output gate. Head sizes of
+// weights = exp(score) / (exp(sink_h) + sum over visible exp(score)); optional output gates per (token, head) and per output number
+// (the sigmoid of a logit, applied in the epilogue). Head sizes of
 // keys (dim) and values (vdim) are independent run-time numbers, grouped-query heads share K/V (head h reads h / (H/G)). The fp32
 // kernels take any size (rows above 256 numbers in key chunks and value column blocks), the tensor-core kernels sizes up to 256.
 // With no window, sink or penalty this is plain causal attention; with v_pool == k_pool and v_ld == dim the value of a token is

@@ -2,7 +2,8 @@
 // own number of new tokens) against a paged cache: embedding into fp32, RMS norm of a sublayer's OUTPUT fused with the residual
 // add, per-head query/key RMS norm fused with value mixing, the output-gate sigmoid and the paged K/V write, the clamped
 // gated-linear activation, the mixture-of-experts router (logits, top-k, softmax over the chosen), the expert sort and the
-// weighted combine, and the distance-penalty table of the biased attention. Everything here is fp32 arithmetic; only the
+// weighted combine, the distance tables of the biased attention (logarithmic and linear), and the embedding that adds the row of
+// a hashed (previous, current) token pair, with the previous token kept per sequence slot. Everything here is fp32 arithmetic; only the
 // storage type of activations ("act": bf16 or fp32) and of the cache differs between the serving mode and the all-fp32 mode.
 #include "common.cuh"
 #include "../../include/phi3_b200.h"
